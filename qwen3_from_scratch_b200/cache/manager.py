@@ -91,6 +91,9 @@ def layout_of(cache_specs: Dict[int, object]) -> CacheLayout:
             names = [p.name for p in spec.planes]
             if not names or len(set(names)) != len(names):
                 raise ValueError(f"cache {cache_id}: a paged cache needs planes with distinct names, got {names}")
+            if spec.entry_tokens < 1 or (spec.entry_tokens > 1 and spec.window is not None):
+                raise ValueError(f"cache {cache_id}: entry_tokens must be positive, and a cache with one entry for "
+                                 f"several tokens has no window (got {spec.entry_tokens}, window {spec.window})")
             if spec not in by_spec:
                 by_spec[spec] = PageGroup(spec, [])
                 layout.groups.append(by_spec[spec])
@@ -195,7 +198,12 @@ class CacheManager:
         """Tokens one request could hold if it had the cache to itself."""
         if not self._pools:
             return 1 << 62
-        return min(p.num_pages for p in self._pools) * self.page_size
+        return min(p.num_pages * g.spec.entry_tokens for p, g in zip(self._pools, self.layout.groups)) * self.page_size
+
+    def _entries(self, group: int, length: int) -> int:
+        """Slots of a group that ``length`` tokens fill: one per token, or one per whole group of
+        ``entry_tokens`` tokens."""
+        return length // self.layout.groups[group].spec.entry_tokens
 
     def _first_needed_page(self, group: int, length: int) -> int:
         """First logical page a query at position >= ``length`` can still read."""
@@ -207,9 +215,10 @@ class CacheManager:
     def pages_needed(self, req: Hashable, new_length: int) -> List[int]:
         """Per group, how many more pages ``req`` needs to hold ``new_length`` tokens."""
         r = self._requests[req]
-        last = (new_length - 1) // self.page_size if new_length > 0 else -1
         need = []
         for g in range(len(self._pools)):
+            entries = self._entries(g, new_length)
+            last = (entries - 1) // self.page_size if entries > 0 else -1
             have = len(r.tables[g])
             need.append(max(0, last + 1 - have))
         return need
@@ -254,7 +263,8 @@ class CacheManager:
         r = self._requests[req]
         if new_length < r.length:
             raise CacheError(f"request {req!r} cannot shrink from {r.length} to {new_length}")
-        if new_length > 0 and any((new_length - 1) // self.page_size >= len(t) for t in r.tables):
+        if any(self._entries(g, new_length) > 0 and (self._entries(g, new_length) - 1) // self.page_size >= len(t)
+               for g, t in enumerate(r.tables)):
             raise CacheError(f"request {req!r} advanced to {new_length} tokens beyond its reserved pages")
         r.length = new_length
         for g, pool in enumerate(self._pools):

@@ -53,10 +53,10 @@ __global__ void swiglu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, 
 }  // namespace q3
 
 // gate_up: [T, 2I]; out: [T, I]; both in `dtype`.  interleave8: columns 16j..16j+7 gate, 16j+8..16j+15 up.
-// act: Q3_ACT_SILU, Q3_ACT_RELU or Q3_ACT_GELU_TANH, applied to the gate.
+// act: Q3_ACT_SILU, Q3_ACT_RELU, Q3_ACT_GELU_TANH or Q3_ACT_RELU_SQ, applied to the gate.
 extern "C" int q3_gated_act(const void* gate_up, void* out, int dtype, int T, int I, int interleave8, int act,
                             cudaStream_t stream) {
-  if (act < Q3_ACT_SILU || act > Q3_ACT_GELU_TANH) return Q3_ERR_SIZE;
+  if (act < Q3_ACT_SILU || (act > Q3_ACT_GELU_TANH && act != Q3_ACT_RELU_SQ)) return Q3_ERR_SIZE;
   if (T <= 0 || I <= 0) return 0;
   if (interleave8 && I % 8) return Q3_ERR_SIZE;
   const size_t total = (size_t)T * I;
@@ -118,7 +118,7 @@ __global__ void act_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bflo
 
 // out = act(x) over `total` values in `dtype`; out may be x.
 extern "C" int q3_act(const void* x, void* out, int dtype, long long total, int act, cudaStream_t stream) {
-  if (act < Q3_ACT_SILU || act > Q3_ACT_GELU_TANH) return Q3_ERR_SIZE;
+  if (act < Q3_ACT_SILU || (act > Q3_ACT_GELU_TANH && act != Q3_ACT_RELU_SQ)) return Q3_ERR_SIZE;
   if (total <= 0) return 0;
   const int threads = 256;
   if (dtype == Q3_BF16 && total % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0) {

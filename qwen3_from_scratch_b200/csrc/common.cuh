@@ -86,6 +86,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 #define Q3_ACT_RELU 1
 #define Q3_ACT_GELU_TANH 2
 #define Q3_ACT_NONE 3
+#define Q3_ACT_RELU_SQ 4  // the square of relu
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + expf(-g)); }
 __device__ __forceinline__ float sigmoid_f(float g) { return 1.0f / (1.0f + expf(-g)); }
@@ -98,6 +99,7 @@ __device__ __forceinline__ float activate(float g, int act) {
     case Q3_ACT_SILU: return silu_f(g);
     case Q3_ACT_RELU: return fmaxf(g, 0.f);
     case Q3_ACT_GELU_TANH: return gelu_tanh_f(g);
+    case Q3_ACT_RELU_SQ: { const float r = fmaxf(g, 0.f); return r * r; }
     default: return g;
   }
 }

@@ -330,7 +330,8 @@ static int gemm_skinny_launch(const void* X, const void* W, void* out, int T, in
 extern "C" int q3_gemm_skinny(const void* X, const void* W, void* out, int T, int N, int K, int ldo, int out_f32,
                               int swiglu, cudaStream_t stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (T > 16 || K <= 0 || K % 8 || swiglu < -1 - Q3_ACT_GELU_TANH || swiglu > 1 + Q3_ACT_GELU_TANH ||
+  if (T > 16 || K <= 0 || K % 8 || swiglu < -1 - Q3_ACT_RELU_SQ || swiglu > 1 + Q3_ACT_RELU_SQ || swiglu == 1 + Q3_ACT_NONE ||
+      swiglu == -1 - Q3_ACT_NONE ||
       (swiglu > 0 && (N % 16 || out_f32)))
     return Q3_ERR_SIZE;
   if ((uintptr_t)X % 16 || (uintptr_t)W % 16) return Q3_ERR_ALIGN;

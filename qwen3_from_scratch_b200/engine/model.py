@@ -15,7 +15,7 @@ import torch
 from ..cache.manager import CacheLayout, layout_of
 from ..config.model_config import ModelConfig
 from ..kernels import ops
-from ..parts.base import NEXT_NORM_WEIGHT, STREAM_SUMSQ, ModelSpec, Runtime, StepContext
+from ..parts.base import EMBEDDING_OUTPUT, NEXT_NORM_WEIGHT, STREAM_SUMSQ, ModelSpec, Runtime, StepContext
 from ..registry import build_model_spec, create_part, load_config
 from ..weights.loader import load_weights
 from ..weights.random_init import random_weights_on_device
@@ -86,12 +86,18 @@ class Model:
             layer.setup(rt, weights)
         self.final_norm.setup(rt, weights)
         self.head.setup(rt, weights)
+        self._keeps_embedding = any(getattr(layer, "needs_embedding_output", False) for layer in self.layers)
 
     @torch.inference_mode()
     def step(self, ctx: StepContext) -> torch.Tensor:
         """One batch through every layer of the run order; float32 logits [len(logit_rows), vocab]."""
         ctx.per_step = {}  # what parts share within a step is computed anew (and so is recorded by a graph capture)
         stream = self.embedding.forward(ctx.token_ids)
+        if self._keeps_embedding:  # a block of this model reads the embedding's output again later
+            kept = self.rt.shared("stream.embedding", self.rt.max_tokens, *stream.shape[1:],
+                                  dtype=stream.dtype)[: stream.shape[0]]
+            kept.copy_(stream)
+            ctx.per_step[EMBEDDING_OUTPUT] = kept
         pending = None
         order = self.spec.order
         for i, call in enumerate(order):

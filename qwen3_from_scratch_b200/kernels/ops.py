@@ -141,6 +141,26 @@ _SIGNATURES = {
                         _c_void_p],
     "q3_gated_group_norm": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                             _c_float, _c_void_p],
+    "q3_add_layernorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
+                         _c_float, _c_void_p],
+    "q3_stream_concat": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_input_conv": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
+                      _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "q3_pw_qkv_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float,
+                       _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p,
+                       _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "q3_pool_blocks": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
+                       _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                       _c_void_p, _c_void_p],
+    "q3_pw_attn_ref": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                       _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void_p, _c_void_p],
+    "q3_mingru_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                       _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "q3_moe_route": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                     _c_float, _c_void_p],
+    "q3_moe_pairs": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
 }
 
 
@@ -457,7 +477,7 @@ def attn_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, out:
     _done("attn_ref", code, f"heads {Hq}/{Hkv}, head_dim {D}")
 
 
-ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "none": 3}
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "none": 3, "relu_sq": 4}
 
 
 def activation_code(name: str, gate: bool = False) -> int:
@@ -1635,3 +1655,255 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Te
         _ptr(partial) if splits > 1 else None, T, ctx.num_seqs, ctx.max_q_len, H, rank, rot, float(scale), splits,
         status.data_ptr(), _stream())
     _done("latent_attention (mma)", code, f"heads {H}, rank {rank}, rot {rot}, splits {splits}")
+
+
+# ------------------------------------------------------------------ layer norm and the convolution before a sub-layer
+def add_layernorm(stream: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor,
+                  out: torch.Tensor, eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """stream (float32 [T, W]) += delta in place, then out = (x - mean) / sqrt(var + eps) * weight + bias with var
+    the mean of the squared deviations; ``out`` is float32 or the dtype of ``delta``.  With ``rows`` (int32) the
+    chosen rows are normed into ``out`` [len(rows), W] and the stream is left as it is."""
+    _check("add_layernorm.stream", stream, torch.float32)
+    _check("add_layernorm.weight", weight, torch.float32)
+    _check("add_layernorm.bias", bias, torch.float32)
+    _check("add_layernorm.out", out)
+    T, W = stream.shape
+    n = T if rows is None else rows.numel()
+    dtype = out.dtype if delta is None else delta.dtype
+    if delta is not None:
+        _check("add_layernorm.delta", delta)
+    if rows is not None:
+        _check("add_layernorm.rows", rows, torch.int32)
+    if (tuple(out.shape) != (n, W) or weight.numel() != W or bias.numel() != W or out.dtype not in (torch.float32, dtype)
+            or (delta is not None and tuple(delta.shape) != (T, W))):
+        raise KernelError(f"add_layernorm: stream {tuple(stream.shape)}, delta "
+                          f"{None if delta is None else tuple(delta.shape)}, out {tuple(out.shape)} {out.dtype}")
+    code = library().q3_add_layernorm(stream.data_ptr(), _ptr(delta), weight.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                                      1 if out.dtype == torch.float32 else 0, dtype_tag(dtype), _ptr(rows), n, W, float(eps),
+                                      _stream())
+    _done("add_layernorm", code, f"width {W}")
+
+
+INPUT_CONV_MAX_TAPS = 16  # the kernel keeps a request's tail in registers while it renews it
+
+
+def stream_concat(stream: torch.Tensor, delta: Optional[torch.Tensor], other: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = [stream[t] + delta[t] | other[t]]: two float32 [T, W] tensors side by side in the dtype of ``out``
+    [T, 2 W]; ``delta`` (in that dtype, or None) is added to the first on the way."""
+    _check("stream_concat.stream", stream, torch.float32)
+    _check("stream_concat.other", other, torch.float32)
+    _check("stream_concat.out", out)
+    T, W = stream.shape
+    if delta is not None:
+        _check("stream_concat.delta", delta, out.dtype)
+    if (tuple(other.shape) != (T, W) or tuple(out.shape) != (T, 2 * W)
+            or (delta is not None and tuple(delta.shape) != (T, W))):
+        raise KernelError(f"stream_concat: stream {tuple(stream.shape)}, other {tuple(other.shape)}, out {tuple(out.shape)}")
+    code = library().q3_stream_concat(stream.data_ptr(), _ptr(delta), other.data_ptr(), out.data_ptr(), dtype_tag(out.dtype),
+                                      T, W, _stream())
+    _done("stream_concat", code, f"width {W}")
+
+
+def input_conv(h: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], q_start: torch.Tensor,
+               tok_seq: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor, status: torch.Tensor,
+               renew_state: bool = True) -> None:
+    """out[t, c] = h[t, c] + sum_j weight[c, j] h[t - (K - 1) + j, c] within each request, h float32 [T, C]; what lies
+    before a portion comes from ``state`` (float32 [slots, K - 1, C], zero for a new request; None for K = 1), which is
+    renewed afterwards."""
+    _check("input_conv.h", h, torch.float32)
+    _check("input_conv.weight", weight, torch.float32)
+    _check("input_conv.out", out)
+    for name, t in (("q_start", q_start), ("tok_seq", tok_seq), ("slot_ids", slot_ids)):
+        _check(f"input_conv.{name}", t, torch.int32)
+    T, C = h.shape
+    K = weight.shape[1]
+    if tuple(out.shape) != (T, C) or weight.shape[0] != C or tok_seq.numel() != T or q_start.numel() < num_seqs + 1:
+        raise KernelError(f"input_conv: h {tuple(h.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    slots = 0
+    if K > 1:
+        _check("input_conv.state", state, torch.float32)
+        if state.dim() != 3 or tuple(state.shape[1:]) != (K - 1, C):
+            raise KernelError(f"input_conv: state {tuple(state.shape)} for {K} taps and {C} channels")
+        slots = state.shape[0]
+    code = library().q3_input_conv(h.data_ptr(), weight.data_ptr(), _ptr(state) if K > 1 else None, q_start.data_ptr(),
+                                   tok_seq.data_ptr(), slot_ids.data_ptr(), out.data_ptr(), dtype_tag(out.dtype), T,
+                                   int(num_seqs), C, K, slots, 1 if renew_state else 0, status.data_ptr(), _stream())
+    _done("input_conv", code, f"channels {C}, taps {K}")
+
+
+# ------------------------------------------------------------------ windowed attention over pooled blocks
+def _pw_pages(name: str, k_pages, v_pages, pk_pages, pv_pages, dtype):
+    for n, t in (("k_pages", k_pages), ("v_pages", v_pages), ("pk_pages", pk_pages), ("pv_pages", pv_pages)):
+        _check(f"{name}.{n}", t, dtype)
+    if (k_pages.dim() != 4 or v_pages.shape[:3] != k_pages.shape[:3] or pk_pages.shape[1:] != k_pages.shape[1:]
+            or pv_pages.shape[1:] != v_pages.shape[1:] or pk_pages.shape[0] != pv_pages.shape[0]):
+        raise KernelError(f"{name}: pages k {tuple(k_pages.shape)}, v {tuple(v_pages.shape)}, pooled k "
+                          f"{tuple(pk_pages.shape)}, pooled v {tuple(pv_pages.shape)}")
+
+
+def pw_qkv_post(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, heads: int, kv_heads: int, dim: int, vdim: int,
+                q_norm: torch.Tensor, k_norm: torch.Tensor, eps: float, dims: int, freq: torch.Tensor, magnitude: float,
+                positions: torch.Tensor, tok_seq: torch.Tensor, table: torch.Tensor, q_out: torch.Tensor,
+                k_pages: torch.Tensor, v_pages: torch.Tensor, write_cache: bool, status: torch.Tensor) -> None:
+    """From one product ``proj`` [T, ld] (q at column ``q_col``, k at ``k_col``, v at ``v_col``): RMS norm of the whole q and of
+    the whole k projection (weights ``q_norm`` [heads * dim], ``k_norm`` [kv_heads * dim]), rotation of the first
+    ``dims`` values of every head by position * freq (sines and cosines times ``magnitude``), q to ``q_out``
+    [T, heads, dim], k and v into their pages."""
+    _check("pw_qkv_post.proj", proj)
+    _check("pw_qkv_post.q_out", q_out, proj.dtype)
+    _check("pw_qkv_post.k_pages", k_pages, proj.dtype)
+    _check("pw_qkv_post.v_pages", v_pages, proj.dtype)
+    for name, t in (("q_norm", q_norm), ("k_norm", k_norm), ("freq", freq)):
+        _check(f"pw_qkv_post.{name}", t, torch.float32)
+    for name, t in (("positions", positions), ("tok_seq", tok_seq), ("table", table)):
+        _check(f"pw_qkv_post.{name}", t, torch.int32)
+    T, ld = proj.shape
+    if (tuple(q_out.shape) != (T, heads, dim) or q_norm.numel() != heads * dim or k_norm.numel() != kv_heads * dim
+            or freq.numel() < dims // 2 or k_col + kv_heads * dim > ld or v_col + kv_heads * vdim > ld
+            or q_col < 0 or q_col + heads * dim > ld or k_col < 0 or v_col < 0
+            or tuple(k_pages.shape[1:]) != (kv_heads, k_pages.shape[2], dim)
+            or tuple(v_pages.shape) != (k_pages.shape[0], kv_heads, k_pages.shape[2], vdim)):
+        raise KernelError(f"pw_qkv_post: proj {tuple(proj.shape)}, q_out {tuple(q_out.shape)}, k pages "
+                          f"{tuple(k_pages.shape)}, v pages {tuple(v_pages.shape)}")
+    code = library().q3_pw_qkv_post(proj.data_ptr() + int(q_col) * proj.element_size(), ld, int(k_col) - int(q_col),
+                                    int(v_col) - int(q_col), heads, kv_heads, dim, vdim, q_norm.data_ptr(),
+                                    k_norm.data_ptr(), float(eps), int(dims), freq.data_ptr(), float(magnitude),
+                                    positions.data_ptr(), tok_seq.data_ptr(), table.data_ptr(), table.shape[1],
+                                    k_pages.shape[2], k_pages.shape[0], q_out.data_ptr(), k_pages.data_ptr(),
+                                    v_pages.data_ptr(), 1 if write_cache else 0, dtype_tag(proj.dtype), T, status.data_ptr(),
+                                    _stream())
+    _done("pw_qkv_post", code, f"heads {heads}/{kv_heads}, dim {dim}, vdim {vdim}, rotated {dims}")
+
+
+def pool_blocks(k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor, pv_pages: torch.Tensor,
+                q_start: torch.Tensor, kv_len: torch.Tensor, table: torch.Tensor, ptable: torch.Tensor, num_seqs: int,
+                max_q_len: int, pool: int, status: torch.Tensor) -> None:
+    """For every block of ``pool`` tokens whose last token is one of this step's: the mean of its keys and of its values
+    (as the token pages hold them) into entry ``block index`` of the block pages."""
+    _pw_pages("pool_blocks", k_pages, v_pages, pk_pages, pv_pages, k_pages.dtype)
+    for name, t in (("q_start", q_start), ("kv_len", kv_len), ("table", table), ("ptable", ptable)):
+        _check(f"pool_blocks.{name}", t, torch.int32)
+    max_blocks = (int(max_q_len) + pool - 1) // pool + 1
+    code = library().q3_pool_blocks(k_pages.data_ptr(), v_pages.data_ptr(), pk_pages.data_ptr(), pv_pages.data_ptr(),
+                                    q_start.data_ptr(), kv_len.data_ptr(), table.data_ptr(), table.shape[1], k_pages.shape[0],
+                                    ptable.data_ptr(), ptable.shape[1], pk_pages.shape[0], k_pages.shape[2], k_pages.shape[1],
+                                    k_pages.shape[3], v_pages.shape[3], int(pool), int(num_seqs), max_blocks,
+                                    dtype_tag(k_pages.dtype), status.data_ptr(), _stream())
+    _done("pool_blocks", code, f"pool {pool}")
+
+
+def pw_attn_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor,
+                pv_pages: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor, table: torch.Tensor,
+                ptable: torch.Tensor, out: torch.Tensor, window: int, pool: int, scale: float, softcap: Optional[float],
+                out_scale: float, status: torch.Tensor) -> None:
+    """Softmax attention of q [T, H, D] over the last ``window`` tokens and the pooled blocks before them; head h's
+    result times ``out_scale`` goes to columns h * vdim .. of ``out`` (rows of any pitch: a column view of a wider
+    buffer is taken).  A warp per (token, head), float32 arithmetic, keys one by one."""
+    _check("pw_attn_ref.q", q)
+    _pw_pages("pw_attn_ref", k_pages, v_pages, pk_pages, pv_pages, q.dtype)
+    for name, t in (("positions", positions), ("tok_seq", tok_seq), ("table", table), ("ptable", ptable)):
+        _check(f"pw_attn_ref.{name}", t, torch.int32)
+    T, H, D = q.shape
+    G, Dv = k_pages.shape[1], v_pages.shape[3]
+    if (out.dtype != q.dtype or out.dim() != 2 or out.shape[0] != T or out.shape[1] != H * Dv or out.stride(1) != 1
+            or k_pages.shape[3] != D or not out.is_cuda):
+        raise KernelError(f"pw_attn_ref: q {tuple(q.shape)}, k pages {tuple(k_pages.shape)}, out {tuple(out.shape)} "
+                          f"strides {out.stride()}")
+    code = library().q3_pw_attn_ref(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), pk_pages.data_ptr(),
+                                    pv_pages.data_ptr(), positions.data_ptr(), tok_seq.data_ptr(), table.data_ptr(),
+                                    table.shape[1], k_pages.shape[0], ptable.data_ptr(), ptable.shape[1], pk_pages.shape[0],
+                                    k_pages.shape[2], out.data_ptr(), out.stride(0), dtype_tag(q.dtype), T, H, G, D, Dv,
+                                    int(window), int(pool), float(scale), float(softcap or 0.0), float(out_scale),
+                                    status.data_ptr(), _stream())
+    _done("pw_attn_ref", code, f"heads {H}/{G}, dim {D}, vdim {Dv}")
+
+
+def pooled_window_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor,
+                            pv_pages: torch.Tensor, ctx, table: torch.Tensor, ptable: torch.Tensor, out: torch.Tensor,
+                            window: int, pool: int, scale: float, softcap: Optional[float], out_scale: float,
+                            status: torch.Tensor) -> None:
+    """The attention of a step's batch over windows and pooled blocks, by the kernel that suits dtype and shape."""
+    pw_attn_ref(q, k_pages, v_pages, pk_pages, pv_pages, ctx.positions, ctx.tok_seq, table, ptable, out, window, pool,
+                scale, softcap, out_scale, status)
+
+
+# ------------------------------------------------------------------ a recurrence gated by the current token alone
+def mingru_scan(proj: torch.Tensor, z_col: int, u_col: int, g_col: int, z_bias: torch.Tensor, u_bias: torch.Tensor,
+                state: torch.Tensor, q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor,
+                out_scale: float, status: torch.Tensor) -> None:
+    """z = sigmoid(proj[:, z_col..] + z_bias), u = proj[:, u_col..] + u_bias, candidate = u + 1/2 (u >= 0) or sigmoid(u);
+    S <- (1 - z) S + z candidate per request, token by token (``state`` float32 [slots, C]);
+    out = S * silu(proj[:, g_col..]) * out_scale.  ``out``: [T, C], rows of any pitch."""
+    _check("mingru_scan.proj", proj)
+    _check("mingru_scan.state", state, torch.float32)
+    for name, t in (("z_bias", z_bias), ("u_bias", u_bias)):
+        _check(f"mingru_scan.{name}", t, torch.float32)
+    for name, t in (("q_start", q_start), ("slot_ids", slot_ids)):
+        _check(f"mingru_scan.{name}", t, torch.int32)
+    T, ld = proj.shape
+    C = state.shape[1]
+    if (out.dtype != proj.dtype or out.dim() != 2 or tuple(out.shape) != (T, C) or out.stride(1) != 1 or state.dim() != 2
+            or z_bias.numel() != C or u_bias.numel() != C or max(z_col, u_col, g_col) + C > ld or min(z_col, u_col, g_col) < 0):
+        raise KernelError(f"mingru_scan: proj {tuple(proj.shape)}, columns {z_col}, {u_col}, {g_col}, state "
+                          f"{tuple(state.shape)}, out {tuple(out.shape)}")
+    code = library().q3_mingru_scan(proj.data_ptr(), ld, int(z_col), int(u_col), int(g_col), z_bias.data_ptr(),
+                                    u_bias.data_ptr(), state.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(),
+                                    out.data_ptr(), out.stride(0), dtype_tag(proj.dtype), T, int(num_seqs), C, state.shape[0],
+                                    float(out_scale), status.data_ptr(), _stream())
+    _done("mingru_scan", code, f"channels {C}")
+
+
+# ------------------------------------------------------------------ routed experts
+MOE_MAX_TOP = 32  # experts per token that the routing kernel lists
+
+
+def moe_route(h: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], ids: torch.Tensor, weights: torch.Tensor,
+              scale: float) -> None:
+    """Scores s = sigmoid(h router^T) in float32; ``ids`` [T, top] the experts with the largest s + bias, ``weights``
+    [T, top] their s * scale."""
+    _check("moe_route.h", h)
+    _check("moe_route.router", router, torch.float32)
+    _check("moe_route.ids", ids, torch.int32)
+    _check("moe_route.weights", weights, torch.float32)
+    T, W = h.shape
+    E = router.shape[0]
+    top = ids.shape[1]
+    if bias is not None:
+        _check("moe_route.bias", bias, torch.float32)
+    if (router.shape[1] != W or tuple(ids.shape) != (T, top) or tuple(weights.shape) != (T, top)
+            or (bias is not None and bias.numel() != E)):
+        raise KernelError(f"moe_route: h {tuple(h.shape)}, router {tuple(router.shape)}, ids {tuple(ids.shape)}")
+    code = library().q3_moe_route(h.data_ptr(), router.data_ptr(), _ptr(bias), ids.data_ptr(), weights.data_ptr(),
+                                  dtype_tag(h.dtype), T, W, E, top, float(scale), _stream())
+    _done("moe_route", code, f"experts {E}, top {top}")
+
+
+def moe_pairs(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+              base: Optional[torch.Tensor], act_buf: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out[t] = base[t] + sum_k weights[t, k] down[ids[t, k]] act(up[ids[t, k]] h[t]); up [E, F, W], down [E, W, F];
+    ``act_buf`` [T * top, F] receives the activations.  Every (token, expert) pair streams its expert once."""
+    _check("moe_pairs.h", h)
+    for name, t in (("up", up), ("down", down), ("act_buf", act_buf), ("out", out)):
+        _check(f"moe_pairs.{name}", t, h.dtype)
+    _check("moe_pairs.ids", ids, torch.int32)
+    _check("moe_pairs.weights", weights, torch.float32)
+    T, W = h.shape
+    E, F = up.shape[0], up.shape[1]
+    top = ids.shape[1]
+    if base is not None:
+        _check("moe_pairs.base", base, h.dtype)
+    if (tuple(up.shape) != (E, F, W) or tuple(down.shape) != (E, W, F) or tuple(ids.shape) != (T, top)
+            or tuple(weights.shape) != (T, top) or tuple(act_buf.shape) != (T * top, F) or tuple(out.shape) != (T, W)
+            or (base is not None and tuple(base.shape) != (T, W))):
+        raise KernelError(f"moe_pairs: h {tuple(h.shape)}, up {tuple(up.shape)}, down {tuple(down.shape)}, ids "
+                          f"{tuple(ids.shape)}, activations {tuple(act_buf.shape)}, out {tuple(out.shape)}")
+    code = library().q3_moe_pairs(h.data_ptr(), up.data_ptr(), down.data_ptr(), ids.data_ptr(), weights.data_ptr(),
+                                  _ptr(base), act_buf.data_ptr(), out.data_ptr(), dtype_tag(h.dtype), T, W, F, E, top,
+                                  activation_code(activation, gate=True), _stream())
+    _done("moe_pairs", code, f"experts {E}, top {top}, inner {F}")
+
+
+def routed_experts(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                   base: Optional[torch.Tensor], act_buf: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """The chosen experts of a step's tokens, by the kernels that suit dtype and shape (see ``moe_pairs``)."""
+    moe_pairs(h, up, down, ids, weights, base, act_buf, out, activation)

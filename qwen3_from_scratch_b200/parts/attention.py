@@ -333,3 +333,112 @@ class LatentAttention(Mixer):
         out = self._o[:T]
         ops.gate_heads(o_heads, gate, out)
         return self.o_proj(out)
+
+
+@register_part("mixer", "pooled_window_attention")
+class PooledWindowAttention(Mixer):
+    """Grouped-query softmax attention over a sliding window of tokens and, before the window, one pooled key and
+    value per block of ``pool`` tokens.  With h the input, H heads on G key/value heads (head n reads key/value head
+    n // (H / G)), keys of ``dim`` and values of ``vdim`` values:
+
+        q = rmsnorm_all(W_q h) w_q;  k = rmsnorm_all(W_k h) w_k;  v = W_v h      (one mean over the whole projection)
+        q, k rotated by ``position`` (a part with ``frequencies()``: the first ``dims`` values of every head)
+        score = q . k * scale;  score <- softcap * tanh(score / softcap) if a cap is given
+        position i reads the tokens j with 0 <= i - j < window and block b (tokens b pool .. b pool + pool - 1) once
+        b pool + pool - 1 <= i - window; a block's key is the mean of its keys as the cache holds them, its value the
+        mean of its values; tokens and blocks share one softmax
+        out = W_o concat_heads(softmax(scores) values)
+
+    Two caches per run: pages with one entry per token (planes ``k`` and ``v``; the manager keeps the pages that the
+    last max(window, pool) tokens touch, so that a block's tokens are still there when its last one arrives) and pages
+    with one entry per block (``pooled``: planes ``pk`` and ``pv``).  ``scale`` is used as given.  Norms, angles, scores
+    and weights are float32 in every run.  ``names``: the tensors' names after the part's own."""
+
+    graph_capturable = True
+    splittable = True
+    NAMES = {"q": "q", "k": "k", "v": "v", "q_norm": "q.norm", "k_norm": "k.norm", "out": "o"}
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
+                 window: int, pool: int, norm_eps: float, position: PartSpec, softcap: Optional[float] = None,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"{self.num_heads} query heads are not a multiple of {self.num_kv_heads} kv heads")
+        self.dim, self.vdim = int(dim), int(vdim)
+        self.scale, self.norm_eps = float(scale), float(norm_eps)
+        self.softcap = None if softcap is None else float(softcap)
+        self.window, self.pool = int(window), int(pool)
+        if self.window < 1 or self.pool < 1:
+            raise ValueError(f"attention {name}: window {self.window} and pool {self.pool} must be positive")
+        self.position = create_part("position", position, name=f"{name}.position")
+        n = dict(self.NAMES)
+        n.update(names or {})
+        self.tensors = {k: f"{name}.{v}" for k, v in n.items()}
+
+    def weight_specs(self) -> List[WeightSpec]:
+        t, w, H, G, D, Dv = self.tensors, self.hidden_size, self.num_heads, self.num_kv_heads, self.dim, self.vdim
+        return [WeightSpec(t["q"], (H * D, w)), WeightSpec(t["k"], (G * D, w)), WeightSpec(t["v"], (G * Dv, w)),
+                WeightSpec(t["q_norm"], (H * D,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["k_norm"], (G * D,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["out"], (w, H * Dv))] + self.position.weight_specs()
+
+    def cache_spec(self):
+        G = self.num_kv_heads
+        return {"": PagedCacheSpec((CachePlane("k", G, self.dim), CachePlane("v", G, self.vdim)),
+                                   window=max(self.window, self.pool)),
+                "pooled": PagedCacheSpec((CachePlane("pk", G, self.dim), CachePlane("pv", G, self.vdim)),
+                                         entry_tokens=self.pool)}
+
+    # ------------------------------------------------------------------ the two products and what lies between
+    def input_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        t = self.tensors
+        q, k, v = weights.pop(t["q"]), weights.pop(t["k"]), weights.pop(t["v"])
+        dtype = torch.float32 if torch.float32 in (q.dtype, k.dtype, v.dtype) else q.dtype
+        return torch.cat([q.to(dtype), k.to(dtype), v.to(dtype)], dim=0)  # columns of the product: q, k, v
+
+    def output_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        return weights.pop(self.tensors["out"])
+
+    @property
+    def input_rows(self) -> int:
+        return (self.num_heads + self.num_kv_heads) * self.dim + self.num_kv_heads * self.vdim
+
+    @property
+    def output_columns(self) -> int:
+        return self.num_heads * self.vdim
+
+    def setup_core(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        self.rt = rt
+        self.q_norm, self.k_norm = weights[self.tensors["q_norm"]], weights[self.tensors["k_norm"]]
+        self.position.setup(rt, weights)
+        self._q = rt.shared("pwattn.q", rt.max_tokens, self.num_heads, self.dim)
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        self.in_proj = Linear(self.input_weight(weights), rt, tag="pwattn.in")
+        self.out_proj = Linear(self.output_weight(weights), rt, tag="pwattn.out")
+        self.setup_core(rt, weights)
+        self._o = rt.shared("pwattn.o", rt.max_tokens, self.output_columns)
+
+    def core(self, proj: torch.Tensor, column: int, ctx: StepContext, cache_id: Optional[int], write_cache: bool,
+             out: torch.Tensor, out_scale: float) -> None:
+        T, H, G, D, Dv = proj.shape[0], self.num_heads, self.num_kv_heads, self.dim, self.vdim
+        planes, table = ctx.pages(cache_id)
+        pooled, ptable = ctx.pages(cache_id, "pooled")
+        freq, mag, dims = self.position.frequencies()
+        status = self.rt.status
+        q = self._q[:T]
+        ops.pw_qkv_post(proj, column, column + H * D, column + (H + G) * D, H, G, D, Dv, self.q_norm, self.k_norm,
+                        self.norm_eps, dims, freq, mag, ctx.positions, ctx.tok_seq, table, q, planes["k"], planes["v"],
+                        write_cache, status)
+        if write_cache:
+            ops.pool_blocks(planes["k"], planes["v"], pooled["pk"], pooled["pv"], ctx.q_start, ctx.kv_len, table, ptable,
+                            ctx.num_seqs, ctx.max_q_len, self.pool, status)
+        ops.pooled_window_attention(q, planes["k"], planes["v"], pooled["pk"], pooled["pv"], ctx, table, ptable, out,
+                                    self.window, self.pool, self.scale, self.softcap, out_scale, status)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        o = self._o[: x.shape[0]]
+        self.core(self.in_proj(x), 0, ctx, cache_id, write_cache, o, 1.0)
+        return self.out_proj(o)

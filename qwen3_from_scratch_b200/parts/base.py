@@ -82,10 +82,13 @@ class PagedCacheSpec:
     latent vector per token; keys and values of different widths; ...).  A plane's pages are one tensor
     ``[num_pages, heads, page_size, width]``; all planes of a cache share the page ids.
     ``window`` = how many of the latest tokens a query still reads (None: all of them); pages a window
-    has passed are given back."""
+    has passed are given back.  ``entry_tokens`` = how many tokens share one slot: with n > 1 the cache holds one
+    entry per whole group of n tokens (entry e belongs to the tokens e n .. e n + n - 1 and exists once the last of
+    them has been computed), for parts that keep a summary per block of tokens; such a cache has no window."""
 
     planes: Tuple[CachePlane, ...]
     window: Optional[int] = None
+    entry_tokens: int = 1
 
     def bytes_per_token(self, compute_itemsize: int) -> int:
         return sum(p.heads * p.width * (4 if p.dtype == "float32" else compute_itemsize) for p in self.planes)
@@ -202,6 +205,7 @@ class StepContext:
 # ---------------------------------------------------------------------- a norm that is not computed
 
 
+EMBEDDING_OUTPUT = "embedding.output"  # key in StepContext.per_step: a copy of what the embedding wrote (float32)
 STREAM_SUMSQ = "stream.sumsq"  # key in StepContext.per_step: StreamStats of the stream as it stands
 NEXT_NORM_WEIGHT = "stream.next_norm_weight"  # key in StepContext.per_step: weight of the next block's first norm
 
@@ -309,6 +313,25 @@ class Mixer(Part):
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         raise NotImplementedError
 
+    #: A mixer that is one product of its input, a core and one product to its output may set this and offer the three
+    #: methods below; the ``parallel`` mixer then runs it beside others on one merged input product and one merged
+    #: output product.
+    splittable = False
+
+    def input_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """Takes (pops) the matrices that read the mixer's input, as one ``[rows, hidden]`` matrix."""
+        raise NotImplementedError
+
+    def output_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        """Takes (pops) the matrix ``[hidden, columns]`` that brings the core's result out."""
+        raise NotImplementedError
+
+    def core(self, proj: torch.Tensor, column: int, ctx: StepContext, cache_id: Optional[int], write_cache: bool,
+             out: torch.Tensor, out_scale: float) -> None:
+        """Everything between the two products: ``proj`` [T, any] holds the input product at ``column``; ``out``
+        (a [T, columns] view of a possibly wider buffer) receives the result times ``out_scale``."""
+        raise NotImplementedError
+
     #: a mixer (or feed-forward) that sets this also has ``can_fuse_stream(rows)``; where that is true its
     #: ``forward`` takes a ``StreamNorm`` for ``x`` and ``into_stream=stream`` (with ``next_norm_weight``, the
     #: weight of the norm that will read the stream next, or None), adds its output into the stream itself and
@@ -329,6 +352,9 @@ class Block(Part):
     #: a block that sets this leaves ``ctx.per_step[STREAM_SUMSQ]`` describing the stream as it returns it
     #: (and returns no pending output); after any other block the model drops the entry
     keeps_stream_stats = False
+
+    #: a block that sets this reads ``ctx.per_step[EMBEDDING_OUTPUT]``; the model then keeps that copy every step
+    needs_embedding_output = False
 
     def cache_spec(self) -> Union[CacheSpec, Dict[str, CacheSpec]]:
         """What one run of the block keeps per request: its mixer's needs, and for a block with state of its

@@ -19,34 +19,89 @@ import torch
 
 from ..registry import create_part, register_part
 from ..kernels import ops
-from .base import (NEXT_NORM_WEIGHT, STREAM_SUMSQ, Block, PartSpec, PendingStreamWrite, Runtime, StateSpec, StepContext,
+from .base import (EMBEDDING_OUTPUT, NEXT_NORM_WEIGHT, STREAM_SUMSQ, Block, PartSpec, PendingStreamWrite, Runtime, StateSpec, StepContext,
                    WeightSpec)
+from .linear import Linear
 
 
 @register_part("block", "pre_norm")
 class PreNormBlock(Block):
-    def __init__(self, name: str, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, feed_forward: PartSpec,
-                 names: Optional[Dict[str, str]] = None):
+    """x <- x + mixer(norm1(x)); x <- x + feed_forward(norm2(x)).  Options, all off by default:
+
+    ``feed_forward`` (and ``norm2``) None: the block is the mixer alone.
+    ``conv_taps`` = K: what each sub-layer reads, h, is first replaced by h + conv(h), a causal convolution over time
+    on each channel with the tensors ``<name>.<conv1>`` (mixer) and ``<name>.<conv2>`` (feed-forward) of shape
+    [width, K]: conv(h)_t = sum_j w[:, j] h_(t - K + 1 + j), zeros before the sequence's start.  The last K - 1
+    inputs of both are kept per request in state slots of the block's own (``conv1``, ``conv2`` in its cache needs).
+    The norm's result stays float32 until the convolution has run.
+    ``reentry``: the full name of a tensor [width, 2 width]; before its first norm the block replaces the stream by
+    W [stream | embedding output] (the model keeps the embedding's output for it)."""
+
+    def __init__(self, name: str, norm1: PartSpec, mixer: PartSpec, norm2: Optional[PartSpec] = None,
+                 feed_forward: Optional[PartSpec] = None, names: Optional[Dict[str, str]] = None,
+                 conv_taps: Optional[int] = None, reentry: Optional[str] = None, width: int = 0):
         super().__init__(name)
-        n = {"norm1": "norm1", "mixer": "mixer", "norm2": "norm2", "feed_forward": "feed_forward"}
+        n = {"norm1": "norm1", "mixer": "mixer", "norm2": "norm2", "feed_forward": "feed_forward", "conv1": "conv1",
+             "conv2": "conv2"}
         n.update(names or {})
         self.norm1 = create_part("norm", norm1, name=f"{name}.{n['norm1']}")
         self.mixer = create_part("mixer", mixer, name=f"{name}.{n['mixer']}")
-        self.norm2 = create_part("norm", norm2, name=f"{name}.{n['norm2']}")
-        self.feed_forward = create_part("feed_forward", feed_forward, name=f"{name}.{n['feed_forward']}")
+        self.norm2 = self.feed_forward = None
+        if feed_forward is not None:
+            if norm2 is None:
+                raise ValueError(f"block {name}: a feed-forward needs the norm before it")
+            self.norm2 = create_part("norm", norm2, name=f"{name}.{n['norm2']}")
+            self.feed_forward = create_part("feed_forward", feed_forward, name=f"{name}.{n['feed_forward']}")
+        self.conv_taps = None if conv_taps is None else int(conv_taps)
+        self.reentry = reentry
+        self.width = int(width)
+        self.conv_tensors = [f"{name}.{n['conv1']}", f"{name}.{n['conv2']}"]
+        if self.conv_taps is not None and not 1 <= self.conv_taps <= ops.INPUT_CONV_MAX_TAPS:
+            raise ValueError(f"block {name}: between 1 and {ops.INPUT_CONV_MAX_TAPS} taps, got {self.conv_taps}")
+        if (self.conv_taps is not None or self.reentry) and self.width <= 0:
+            raise ValueError(f"block {name}: needs the stream's width")
+        if self.conv_taps is not None and not hasattr(self.norm1, "add_norm_float32"):
+            raise ValueError(f"block {name}: the convolution reads a norm that can leave float32 rows (add_norm_float32)")
+        self.needs_embedding_output = bool(self.reentry)
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.feed_forward) if p is not None]
 
     @property
     def graph_capturable(self) -> bool:
-        return all(p.graph_capturable for p in (self.norm1, self.mixer, self.norm2, self.feed_forward))
+        return all(p.graph_capturable for p in self._parts())
 
     def weight_specs(self) -> List[WeightSpec]:
-        return (self.norm1.weight_specs() + self.mixer.weight_specs() + self.norm2.weight_specs()
-                + self.feed_forward.weight_specs())
+        specs = [s for p in self._parts() for s in p.weight_specs()]
+        if self.conv_taps is not None:
+            for tensor in self.conv_tensors[: 2 if self.feed_forward is not None else 1]:
+                specs.append(WeightSpec(tensor, (self.width, self.conv_taps), kind="vector", init="normal"))
+        if self.reentry:
+            specs.append(WeightSpec(self.reentry, (self.width, 2 * self.width)))
+        return specs
+
+    def cache_spec(self):
+        need = self.mixer.cache_spec()
+        if self.conv_taps is None or self.conv_taps == 1:
+            return need
+        needs = dict(need) if isinstance(need, dict) else ({} if need is None else {"": need})
+        for label in ["conv1", "conv2"][: 2 if self.feed_forward is not None else 1]:
+            if label in needs:
+                raise ValueError(f"block {self.name}: its mixer already keeps something called '{label}'")
+            needs[label] = StateSpec((self.conv_taps - 1, self.width), "float32")
+        return needs
 
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
-        for part in (self.norm1, self.mixer, self.norm2, self.feed_forward):
+        for part in self._parts():
             part.setup(rt, weights)
+        if self.conv_taps is not None:
+            self.conv_weights = [weights[t] for t in self.conv_tensors[: 2 if self.feed_forward is not None else 1]]
+            self._conv_out = rt.shared("block.conv_out", rt.max_tokens, self.width)
+        if self.reentry:
+            # layers that run again (a looped span) share the tensor: every block that names it takes the same one
+            self.reentry_proj = Linear(weights[self.reentry], rt, tag="block.reentry", out_dtype=torch.float32)
+            self._both = rt.shared("block.reentry_in", rt.max_tokens, 2 * self.width)
 
     keeps_stream_stats = True
 
@@ -54,14 +109,26 @@ class PreNormBlock(Block):
     def first_norm_weight(self) -> Optional[torch.Tensor]:
         """The weight of the norm this block applies to the stream first, if the block before may prepare
         the stream for it (see StreamStats.scaled)."""
-        return self.norm1.weight if hasattr(self.norm1, "lazy") else None
+        return self.norm1.weight if hasattr(self.norm1, "lazy") and not self.reentry else None
 
     def fuses(self, rows: int) -> bool:
         """A few rows (decoding) in bfloat16: the mixer's and the feed-forward's last projections add into
         the stream themselves and their first ones apply the norm, so that no norm kernel runs."""
-        return (self.rt.dtype == torch.bfloat16 and hasattr(self.norm1, "lazy") and hasattr(self.norm2, "lazy")
+        return (self.rt.dtype == torch.bfloat16 and self.feed_forward is not None and self.conv_taps is None
+                and not self.reentry and hasattr(self.norm1, "lazy") and hasattr(self.norm2, "lazy")
                 and getattr(self.mixer, "fuses_stream", False) and getattr(self.feed_forward, "fuses_stream", False)
                 and self.mixer.can_fuse_stream(rows) and self.feed_forward.can_fuse_stream(rows))
+
+    def _read(self, which: int, norm, stream: torch.Tensor, pending, ctx: StepContext, cache_id) -> torch.Tensor:
+        """What sub-layer ``which`` reads: the normed stream, through the convolution if the block has one."""
+        if self.conv_taps is None:
+            return norm.add_norm(stream, pending)
+        h = norm.add_norm_float32(stream, pending)
+        out = self._conv_out[: stream.shape[0]]
+        state = ctx.state(cache_id, ("conv1", "conv2")[which]) if self.conv_taps > 1 else None
+        ops.input_conv(h, self.conv_weights[which], state, ctx.q_start, ctx.tok_seq, ctx.slot_ids, ctx.num_seqs, out,
+                       self.rt.status)
+        return out
 
     def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx: StepContext,
                 cache_id: Optional[int], write_cache: bool) -> Optional[torch.Tensor]:
@@ -76,9 +143,16 @@ class PreNormBlock(Block):
             shared[STREAM_SUMSQ] = self.feed_forward.forward(self.norm2.lazy(stream, stats), into_stream=stream,
                                                              next_norm_weight=shared.get(NEXT_NORM_WEIGHT))
             return None
-        x = self.norm1.add_norm(stream, pending)
+        if self.reentry:
+            both = self._both[: stream.shape[0]]
+            ops.stream_concat(stream, pending, shared[EMBEDDING_OUTPUT], both)
+            stream.copy_(self.reentry_proj(both))
+            pending = None
+        x = self._read(0, self.norm1, stream, pending, ctx, cache_id)
         a = self.mixer.forward(x, ctx, cache_id, write_cache)
-        x = self.norm2.add_norm(stream, a)
+        if self.feed_forward is None:
+            return a
+        x = self._read(1, self.norm2, stream, a, ctx, cache_id)
         return self.feed_forward.forward(x)
 
 

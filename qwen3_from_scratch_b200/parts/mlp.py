@@ -13,8 +13,8 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from ..registry import register_part
-from .base import FeedForward, Runtime, StreamNorm, WeightSpec
+from ..registry import create_part, register_part
+from .base import FeedForward, PartSpec, Runtime, StreamNorm, WeightSpec
 from .linear import Linear
 
 _DEFAULT_NAMES = {"gate": "gate_proj.weight", "up": "up_proj.weight", "down": "down_proj.weight"}
@@ -133,3 +133,73 @@ class DenseMLP(FeedForward):
         h = self.up(x)
         ops.act(h, h, self.activation)
         return self.down(h)
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(FeedForward):
+    """A mixture of experts: ``experts`` small feed-forwards W_down act(W_up h) without biases, of which every token
+    uses ``top``.
+
+        s = sigmoid(W_router h)                  float32 (h may be its rounding to the compute dtype)
+        chosen: the ``top`` experts with the largest s + correction (ties: the lower index)
+        y = sum_chosen s_e * router_scale * expert_e(h)  [+ shared(h)]
+
+    The correction takes part in the choice only; the weights are not renormalised.  ``shared``: a feed-forward
+    (any registered one) that every token goes through, added to the sum, or None.  Tensors: ``<name>.<router>``
+    [E, width], ``<name>.<correction>`` [E] (absent with ``correction=False``), ``<name>.<expert><e>.<up>`` [ff, width]
+    and ``.<down>`` [width, ff], and the shared part's under ``<name>.<shared>``."""
+
+    graph_capturable = True
+    NAMES = {"router": "router", "correction": "correction", "expert": "e", "up": "up", "down": "down", "shared": "shared"}
+
+    def __init__(self, name: str, hidden_size: int, experts: int, top: int, expert_ff: int, router_scale: float = 1.0,
+                 activation: str = "relu_sq", correction: bool = True, shared: Optional[PartSpec] = None,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.experts, self.top, self.expert_ff = int(hidden_size), int(experts), int(top), int(expert_ff)
+        if not 1 <= self.top <= min(self.experts, ops.MOE_MAX_TOP):
+            raise ValueError(f"feed-forward {name}: top {self.top} of {self.experts} experts (at most {ops.MOE_MAX_TOP})")
+        self.router_scale = float(router_scale)
+        ops.activation_code(activation, gate=True)
+        self.activation = activation
+        self.has_correction = bool(correction)
+        n = dict(self.NAMES)
+        n.update(names or {})
+        self.n = n
+        self.shared = None if shared is None else create_part("feed_forward", shared, name=f"{name}.{n['shared']}")
+
+    def _expert(self, e: int, which: str) -> str:
+        return f"{self.name}.{self.n['expert']}{e}.{self.n[which]}"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        w, f = self.hidden_size, self.expert_ff
+        specs = [WeightSpec(f"{self.name}.{self.n['router']}", (self.experts, w), kind="vector", init="normal")]
+        if self.has_correction:
+            specs.append(WeightSpec(f"{self.name}.{self.n['correction']}", (self.experts,), kind="vector", init="normal"))
+        for e in range(self.experts):
+            specs += [WeightSpec(self._expert(e, "up"), (f, w)), WeightSpec(self._expert(e, "down"), (w, f))]
+        return specs + (self.shared.weight_specs() if self.shared is not None else [])
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        self.router = weights[f"{self.name}.{self.n['router']}"]
+        self.correction = weights[f"{self.name}.{self.n['correction']}"] if self.has_correction else None
+        # the experts' matrices in two stacks, in the compute dtype: up [E, ff, width], down [E, width, ff]
+        self.up = torch.stack([weights.pop(self._expert(e, "up")).to(rt.dtype) for e in range(self.experts)]).contiguous()
+        self.down = torch.stack([weights.pop(self._expert(e, "down")).to(rt.dtype) for e in range(self.experts)]).contiguous()
+        if self.shared is not None:
+            self.shared.setup(rt, weights)
+        T = rt.max_tokens
+        self._ids = rt.shared("moe.ids", T, self.top, dtype=torch.int32)
+        self._weights = rt.shared("moe.weights", T, self.top, dtype=torch.float32)
+        self._act = rt.shared("moe.act", T * self.top, self.expert_ff)
+        self._out = rt.shared("moe.out", T, self.hidden_size)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        T = x.shape[0]
+        ids, wts = self._ids[:T], self._weights[:T]
+        ops.moe_route(x, self.router, self.correction, ids, wts, self.router_scale)
+        base = self.shared.forward(x) if self.shared is not None else None
+        out = self._out[:T]
+        ops.routed_experts(x, self.up, self.down, ids, wts, base, self._act[: T * self.top], out, self.activation)
+        return out

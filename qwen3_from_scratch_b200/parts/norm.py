@@ -1,4 +1,4 @@
-"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, statistics in float32.
+"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, and layer norm with weight and bias; statistics in float32.
 
 Reference: models/norm.py:11-22 (weight multiplies directly, eps from the configuration),
 csrc/rms_norm/rms_norm.cpp:13-31.
@@ -92,4 +92,52 @@ class StreamSumRMSNorm(Norm):
         out = torch.empty(rows.numel(), self.dim, dtype=self.rt.dtype, device=stream.device)
         pending = None if delta is None else (delta.delta, delta.mix, delta.write)
         ops.hc_sum_norm_rows(stream, pending, self.weight, rows, out, self.eps, self.rt.status)
+        return out
+
+
+@register_part("norm", "layer_norm")
+class LayerNorm(Norm):
+    """y = (x - mean) / sqrt(var + eps) * w + b over the last axis, var the mean of the squared deviations; statistics
+    in float32.  The weight is the tensor ``<name><suffix>``, the bias ``<name><bias_suffix>``.  ``add_norm`` returns
+    the compute dtype; ``add_norm_float32`` the same rows in float32, for a block that works on the normed rows
+    before it hands them to a projection."""
+
+    graph_capturable = True
+
+    def __init__(self, name: str, dim: int, eps: float, suffix: str = ".weight", bias_suffix: str = ".bias"):
+        super().__init__(name)
+        self.dim, self.eps = int(dim), float(eps)
+        self.tensor, self.bias_tensor = f"{name}{suffix}", f"{name}{bias_suffix}"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.tensor, (self.dim,), kind="vector", init="one_plus_normal"),
+                WeightSpec(self.bias_tensor, (self.dim,), kind="vector", init="normal")]
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        self.weight, self.bias = weights[self.tensor], weights[self.bias_tensor]
+        self._out = rt.shared("normed", rt.max_tokens, self.dim)
+        self._out32 = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        stream = x.to(torch.float32).contiguous()
+        out = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        ops.add_layernorm(stream, None, self.weight, self.bias, out, self.eps)
+        return out
+
+    def add_norm(self, stream: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        out = self._out[: stream.shape[0]]
+        ops.add_layernorm(stream, delta, self.weight, self.bias, out, self.eps)
+        return out
+
+    def add_norm_float32(self, stream: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
+        if self._out32 is None:
+            self._out32 = self.rt.shared("normed.float32", self.rt.max_tokens, self.dim, dtype=torch.float32)
+        out = self._out32[: stream.shape[0]]
+        ops.add_layernorm(stream, delta, self.weight, self.bias, out, self.eps)
+        return out
+
+    def norm_rows(self, stream: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(rows.numel(), self.dim, dtype=self.rt.dtype, device=stream.device)
+        ops.add_layernorm(stream, delta, self.weight, self.bias, out, self.eps, rows=rows)
         return out

@@ -252,3 +252,72 @@ class SSD(Mixer, _NamedTensors):
         gated = self._gated[:T]
         ops.gated_group_norm(y, proj, 0, self.norm_weight, gated, self.norm_groups, self.norm_eps)
         return self.out_proj(gated)
+
+
+@register_part("mixer", "mingru")
+class MinGRU(Mixer, _NamedTensors):
+    """A gated recurrence whose gates read only the current token (the minGRU of Feng et al., "Were RNNs All We
+    Needed?", with the candidate's activation continued linearly above zero).  With h the input and C channels:
+
+        z = sigmoid(W_z h + b_z);  u = W_x h + b_x;  candidate = u + 1/2 where u >= 0, sigmoid(u) where u < 0
+        S_t = (1 - z) S_(t-1) + z candidate      element by element, S float32, zero for a new request
+        out = W_o (S_t silu(W_g h))
+
+    Everything but the projections is float32.  ``names``: the tensors' names after the part's own."""
+
+    graph_capturable = True
+    splittable = True
+    NAMES = {"z": "z", "z_bias": "z.b", "x": "x", "x_bias": "x.b", "gate": "g", "out": "o"}
+
+    def __init__(self, name: str, hidden_size: int, width: int, names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.width = int(hidden_size), int(width)
+        self._name_tensors(name, self.NAMES, names)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        t, h, c = self.tensors, self.hidden_size, self.width
+        return [WeightSpec(t["z"], (c, h)), WeightSpec(t["z_bias"], (c,), kind="vector", init="normal"),
+                WeightSpec(t["x"], (c, h)), WeightSpec(t["x_bias"], (c,), kind="vector", init="normal"),
+                WeightSpec(t["gate"], (c, h)), WeightSpec(t["out"], (h, c))]
+
+    def cache_spec(self):
+        return StateSpec((self.width,), "float32")
+
+    def input_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        t = self.tensors
+        z, x, g = weights.pop(t["z"]), weights.pop(t["x"]), weights.pop(t["gate"])
+        dtype = torch.float32 if torch.float32 in (z.dtype, x.dtype, g.dtype) else z.dtype
+        return torch.cat([z.to(dtype), x.to(dtype), g.to(dtype)], dim=0)  # columns of the product: z, u, g
+
+    def output_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        return weights.pop(self.tensors["out"])
+
+    @property
+    def input_rows(self) -> int:
+        return 3 * self.width
+
+    @property
+    def output_columns(self) -> int:
+        return self.width
+
+    def setup_core(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        self.rt = rt
+        self.z_bias, self.x_bias = weights[self.tensors["z_bias"]], weights[self.tensors["x_bias"]]
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        self.in_proj = Linear(self.input_weight(weights), rt, tag="mingru.in")
+        self.out_proj = Linear(self.output_weight(weights), rt, tag="mingru.out")
+        self.setup_core(rt, weights)
+        self._gated = rt.shared("mingru.gated", rt.max_tokens, self.width)
+
+    def core(self, proj: torch.Tensor, column: int, ctx: StepContext, cache_id: Optional[int], write_cache: bool,
+             out: torch.Tensor, out_scale: float) -> None:
+        c = self.width
+        ops.mingru_scan(proj, column, column + c, column + 2 * c, self.z_bias, self.x_bias, ctx.state(cache_id),
+                        ctx.q_start, ctx.slot_ids, ctx.num_seqs, out, out_scale, self.rt.status)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        gated = self._gated[: x.shape[0]]
+        self.core(self.in_proj(x), 0, ctx, cache_id, write_cache, gated, 1.0)
+        return self.out_proj(gated)

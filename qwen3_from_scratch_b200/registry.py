@@ -105,5 +105,5 @@ def _load_builtin() -> None:
     global _builtin_loaded
     if not _builtin_loaded:
         _builtin_loaded = True
-        from .parts import attention, block, embedding, mlp, norm, recurrent, rope  # noqa: F401  register themselves
-        from .models import bikadra, binupel, qwen3  # noqa: F401  register the architectures
+        from .parts import attention, block, embedding, mlp, norm, parallel, recurrent, rope  # noqa: F401  register themselves
+        from .models import bikadra, binupel, dogidra, qwen3  # noqa: F401  register the architectures
