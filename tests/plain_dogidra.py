@@ -259,3 +259,29 @@ def forward(config: dict, w: Dict[str, torch.Tensor], tokens: Sequence[int], sta
             layers_out.append(x.clone())
     x = layer_norm(x, w["final.norm"], w["final.norm.b"], float(config["norm"]["eps"]))
     return linear(x, w["embed"])
+
+
+def forward_logits(config: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> torch.Tensor:
+    return forward(config, w, ids)
+
+
+def rounding_error(config: dict, w: Dict[str, torch.Tensor], ids: Sequence[int]) -> float:
+    """The largest difference that rounding every projection's operand and result (and the cached keys and values)
+    to bfloat16 makes to a logit of this prompt, relative to the largest logit."""
+    exact = forward(config, w, ids)
+    with bfloat16_projections():
+        rounded = forward(config, w, ids)
+    return float((rounded - exact).abs().max()) / float(exact.abs().max())
+
+
+def greedy(config: dict, w: Dict[str, torch.Tensor], prompt: Sequence[int], new_tokens: int):
+    """(generated ids, gap between the two largest logits at every step), token by token through the states."""
+    state = new_state(config)
+    logits = forward(config, w, prompt, state)
+    out, margins = [], []
+    for _ in range(new_tokens):
+        top = torch.topk(logits[-1], 2).values
+        margins.append(float(top[0] - top[1]))
+        out.append(int(torch.argmax(logits[-1])))
+        logits = forward(config, w, [out[-1]], state)
+    return out, margins
