@@ -1,11 +1,13 @@
-"""``bench.py --arch binupel|bikadra``: another design beside Qwen3 at equal layer sizes (random weights drawn on
+"""``bench.py --arch binupel|bikadra|dogidra``: another design beside Qwen3 at equal layer sizes (random weights drawn on
 the device): a prompt step of 2,048 tokens and decode steps at two batch sizes, each replayed on the device
 between CUDA events, and every kernel of one eagerly launched step timed by events of its own, with the bytes
 or flops it must move and the fraction of the measured copy bandwidth or bf16 throughput that this makes.
 
 A Binupel model of ``layers`` entries repeats the pattern selective scan, RG-LRU, attention; a Bikadra model
-alternates the state-space mixer and attention through a latent, over four residual streams; the Qwen3 model has as
-many layers of the same width, heads, head size and feed-forward width.
+alternates the state-space mixer and attention through a latent, over four residual streams; a Dogidra model runs
+windowed attention over pooled blocks beside a minGRU in every layer, routed experts with a shared one behind them,
+and a span of two layers twice; the Qwen3 model has as many layer runs of the same width, heads, head size and
+(active) feed-forward width.
 """
 
 from __future__ import annotations
@@ -54,6 +56,24 @@ def bikadra_config(s):
     return {"architecture": "Bikadra", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0},
             "streams": 4, "norm": {"eps": 1e-6}, "logit_softcap": 30.0,
             "layers": [pattern[i % 2] for i in range(s["layers"])]}
+
+
+def dogidra_config(s):
+    """Every layer: attention over a window of 1,024 tokens and blocks of 16 beside a minGRU as wide as the stream; 16
+    experts of a quarter of the dense feed-forward's width, three per token, and a shared one of the same width (as
+    many active rows as the dense one); four taps.  Two of the listed layers run twice, so that the layer runs are as
+    many as the other model's layers."""
+    layer = {"type": "parallel",
+             "mixer": {"left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                                "scale": s["dim"] ** -0.5, "softcap": 50.0, "mask": {"size": 1024, "pool": 16},
+                                "rot": {"base": 10000.0, "dims": s["dim"] // 2,
+                                        "scaling": {"factor": 16.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+                       "right": {"width": s["width"]}, "left_scale": 0.7, "right_scale": 0.7},
+             "mlp": {"kind": "moe", "router": {"experts": 16, "top": 3, "scale": 1.0}, "expert": {"ff": s["ff"] // 4},
+                     "shared": {"ff": s["ff"] // 4}}}
+    return {"architecture": "Dogidra", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "loop": {"start": 1, "stop": 3, "times": 2},
+            "layers": [layer] * (s["layers"] - 2)}
 
 
 def qwen3_config(s):
@@ -185,6 +205,43 @@ class KernelClock:
         if name == "gated_group_norm":
             y, out = a[0], a[4]
             return "bytes", size(y) + 2 * size(out)
+        if name == "add_layernorm":
+            stream, delta, out = a[0], a[1], a[4]
+            return "bytes", size(stream) * (2 if delta is not None else 1) + (size(delta) if delta is not None else 0) + size(out)
+        if name == "norm_conv":
+            stream, delta, out = a[0], a[1], a[-2]
+            return "bytes", size(stream) * (2 if delta is not None else 1) + (size(delta) if delta is not None else 0) + size(out)
+        if name == "input_conv":
+            return "bytes", size(a[0]) + size(a[7])
+        if name == "stream_concat":
+            return "bytes", size(a[0]) + size(a[2]) + size(a[3]) + (size(a[1]) if a[1] is not None else 0)
+        if name == "pw_qkv_post":
+            proj, heads, kv_heads, dim, vdim = a[0], a[4], a[5], a[6], a[7]
+            n = proj.shape[0] * proj.element_size()
+            return "bytes", n * (2 * heads * dim + 2 * kv_heads * (dim + vdim))
+        if name == "pool_blocks":
+            k_pages, v_pages = a[0], a[1]
+            n = sc["tokens"] if sc["kind"] == "prefill" else sc["batch"]
+            return "bytes", n * k_pages.shape[1] * (k_pages.shape[3] + v_pages.shape[3]) * k_pages.element_size() * (1 + 1 / a[10])
+        if name == "pooled_window_attention":
+            q, k_pages, v_pages, window, pool = a[0], a[1], a[2], a[9], a[10]
+            H, D = q.shape[1], q.shape[2]
+            G, Dv = k_pages.shape[1], v_pages.shape[3]
+            seen = lambda i: min(i + 1, window) + max(0, i + 1 - window) // pool  # noqa: E731
+            if sc["kind"] == "prefill":
+                return "flops", 2 * H * (D + Dv) * sum(seen(i) for i in range(sc["tokens"]))
+            return "bytes", sc["batch"] * seen(sc["context"] - 1) * G * (D + Dv) * k_pages.element_size() + 2 * size(q)
+        if name == "mingru_scan":
+            out = a[10]
+            return "bytes", 4 * out.numel() * out.element_size()
+        if name == "moe_route":
+            return "bytes", size(a[0]) + size(a[1])
+        if name == "routed_experts":
+            h, up, down, ids = a[0], a[1], a[2], a[3]
+            pairs = ids.numel()
+            if h.shape[0] <= 16:
+                return "bytes", min(pairs, up.shape[0]) * (size(up) + size(down)) // up.shape[0]
+            return "flops", 4 * pairs * up.shape[1] * up.shape[2]
         return "bytes", 0
 
     def wrap(self, owner, attr, name):
@@ -209,7 +266,9 @@ class KernelClock:
                      "gated_act", "swiglu", "qk_gate_post", "qkv_post", "gemm_tc_qkv", "rglru_scan", "selective_scan",
                      "sigmoid_attention", "paged_attention", "block_diag", "gemm_skinny", "gemm_skinny_normed",
                      "gemm_skinny_into_stream", "gemm_tc", "embed_scaled", "hc_norm", "act", "latent_kv_post",
-                     "latent_q_post", "gate_heads", "latent_attention", "ssd_scan", "gated_group_norm"):
+                     "latent_q_post", "gate_heads", "latent_attention", "ssd_scan", "gated_group_norm", "add_layernorm",
+                     "input_conv", "stream_concat", "pw_qkv_post", "pool_blocks", "pooled_window_attention",
+                     "mingru_scan", "moe_route", "routed_experts"):
             self.wrap(ops, name, name)
         real_mm = torch.mm
         clock = self
@@ -296,7 +355,7 @@ def compare(args, peaks, sample_clocks):
                  "decode_b64_ctx2048": {"kind": "decode", "batch": 64, "context": 2048}}
     sampler = sample_clocks()
     t0 = time.time()
-    other = {"binupel": binupel_config, "bikadra": bikadra_config}[args.arch]
+    other = {"binupel": binupel_config, "bikadra": bikadra_config, "dogidra": dogidra_config}[args.arch]
     out = {"arch": args.arch, "beside": "qwen3", "sizes": dict(size, name=args.arch_size), "dtype": "bf16",
            "data": "synthetic tokens, random weights drawn on the device", "steps": args.steps, "warmup": args.warmup,
            "peaks": peaks, "timing": "CUDA events around each replay of the step; 256 MB written between replays",

@@ -117,27 +117,38 @@ __global__ void pool_blocks_kernel(const T* __restrict__ k_pages, const T* __res
   const int* row = table + (size_t)b * stride;
   const int p_in = blk % page_size;
   const float count = (float)P;
-  for (int i = threadIdx.x; i < G * (D + Dv); i += blockDim.x) {
-    const bool is_k = i < G * D;
-    const int e = is_k ? i : i - G * D;
-    const int width = is_k ? D : Dv;
-    const int g = e / width, d = e - g * width;
-    const T* pages = is_k ? k_pages : v_pages;
-    float sum = 0.f;
-    bool bad = false;
-    for (int j = 0; j < P; ++j) {
-      const int pos = blk * P + j;
-      const int page = table_page(row, pos / page_size, stride, status);
+  // one value per thread; the block's tokens are asked for eight at a time, so that the loads overlap
+  const int i = blockIdx.z * blockDim.x + threadIdx.x;
+  if (i >= G * (D + Dv)) return;
+  const bool is_k = i < G * D;
+  const int e = is_k ? i : i - G * D;
+  const int width = is_k ? D : Dv;
+  const int g = e / width, d = e - g * width;
+  const T* pages = is_k ? k_pages : v_pages;
+  float sum = 0.f;
+  bool bad = false;
+  for (int j0 = 0; j0 < P; j0 += 8) {
+    float part[8];
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      const int pos = blk * P + min(j0 + jj, P - 1);
+      int page = table_page(row, pos / page_size, stride, status);
       if (page < 0 || page >= num_pages) {
         bad = true;
-        continue;
+        page = 0;
       }
-      sum += to_float(pages[(((size_t)page * G + g) * page_size + pos % page_size) * width + d]);
+      part[jj] = to_float(pages[(((size_t)page * G + g) * page_size + pos % page_size) * width + d]);
     }
-    if (bad) atomicOr(status, Q3_STATUS_BAD_PAGE);
-    T* dst = is_k ? pk_pages : pv_pages;
-    dst[(((size_t)ppage * G + g) * page_size + p_in) * width + d] = from_float<T>(sum / count);
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj)
+      if (j0 + jj < P) sum += part[jj];
   }
+  if (bad) {
+    atomicOr(status, Q3_STATUS_BAD_PAGE);
+    sum = 0.f;
+  }
+  T* dst = is_k ? pk_pages : pv_pages;
+  dst[(((size_t)ppage * G + g) * page_size + p_in) * width + d] = from_float<T>(sum / count);
 }
 
 template <typename T>
@@ -243,7 +254,7 @@ extern "C" int q3_pool_blocks(const void* k_pages, const void* v_pages, void* pk
                               int max_blocks, int dtype, int* status, cudaStream_t stream) {
   if (B <= 0 || max_blocks <= 0) return 0;
   if (G <= 0 || D <= 0 || Dv <= 0 || P <= 0 || page_size <= 0 || stride <= 0 || pstride <= 0 || B > 65535) return Q3_ERR_SIZE;
-  Q3_BY_DTYPE(dtype, q3::launch(q3::pool_blocks_kernel<E>, dim3(max_blocks, B), dim3(128), 0, stream, (const E*)k_pages,
+  Q3_BY_DTYPE(dtype, q3::launch(q3::pool_blocks_kernel<E>, dim3(max_blocks, B, (G * (D + Dv) + 127) / 128), dim3(128), 0, stream, (const E*)k_pages,
                                 (const E*)v_pages, (E*)pk_pages, (E*)pv_pages, q_start, kv_len, table, stride, num_pages,
                                 ptable, pstride, num_ppages, page_size, G, D, Dv, P, status))
   return q3::launch_status();

@@ -155,8 +155,17 @@ _SIGNATURES = {
     "q3_pw_attn_ref": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
                        _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void_p, _c_void_p],
+    "q3_pw_attn_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                       _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
     "q3_mingru_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+    "q3_moe_grouped": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                       _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                       _c_void_p, _c_void_p],
+    "q3_mingru_scan_chunked": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                               _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                               _c_float, _c_void_p, _c_void_p],
     "q3_moe_route": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_float, _c_void_p],
     "q3_moe_pairs": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
@@ -192,6 +201,8 @@ def library() -> ctypes.CDLL:
                 lib.q3_attn_decode_blocks_per_sm.restype = _c_int
                 lib.q3_latent_attn_mma_takes.argtypes = [_c_int, _c_int]
                 lib.q3_latent_attn_mma_takes.restype = _c_int
+                lib.q3_pw_attn_mma_takes.argtypes = [_c_int, _c_int]
+                lib.q3_pw_attn_mma_takes.restype = _c_int
                 lib.q3_ssd_record_floats.argtypes = [_c_int, _c_int, _c_int]
                 lib.q3_ssd_record_floats.restype = _c_ll
                 lib.q3_ssd_mma_takes.argtypes = [_c_int, _c_int]
@@ -202,6 +213,10 @@ def library() -> ctypes.CDLL:
                 lib.q3_ssd_chunk.restype = _c_int
                 lib.q3_scan_chunk.argtypes = []
                 lib.q3_scan_chunk.restype = _c_int
+                lib.q3_mingru_chunk.argtypes = []
+                lib.q3_mingru_chunk.restype = _c_int
+                lib.q3_moe_tile_rows.argtypes = []
+                lib.q3_moe_tile_rows.restype = _c_int
                 lib.q3_sample_scratch_bytes.argtypes = [_c_int]
                 lib.q3_sample_scratch_bytes.restype = _c_ll
                 _lib, _lib_path = _Counting(lib), path
@@ -1818,22 +1833,77 @@ def pw_attn_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, p
     _done("pw_attn_ref", code, f"heads {H}/{G}, dim {D}, vdim {Dv}")
 
 
+def pw_attention_fast(dtype: torch.dtype, dim: int, vdim: int) -> bool:
+    """Whether the tensor-core kernel takes these heads: bfloat16, keys and values of 32, 64 or 128 values."""
+    return dtype == torch.bfloat16 and bool(library()._lib.q3_pw_attn_mma_takes(int(dim), int(vdim)))
+
+
+def pw_attn_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor,
+                pv_pages: torch.Tensor, ctx, table: torch.Tensor, ptable: torch.Tensor, out: torch.Tensor, window: int,
+                pool: int, scale: float, softcap: Optional[float], out_scale: float, status: torch.Tensor) -> None:
+    """The same attention as ``pw_attn_ref`` on the tensor cores (bfloat16): tiles of 64 entries of the block pages
+    and of the token pages in one online softmax, 128 (token, head) rows of one kv head to a block."""
+    _check("pw_attn_mma.q", q, torch.bfloat16)
+    _pw_pages("pw_attn_mma", k_pages, v_pages, pk_pages, pv_pages, q.dtype)
+    for name, t in (("q_start", ctx.q_start), ("kv_len", ctx.kv_len), ("table", table), ("ptable", ptable)):
+        _check(f"pw_attn_mma.{name}", t, torch.int32)
+    T, H, D = q.shape
+    G, Dv = k_pages.shape[1], v_pages.shape[3]
+    if (out.dtype != q.dtype or out.dim() != 2 or out.shape[0] != T or out.shape[1] != H * Dv or out.stride(1) != 1
+            or k_pages.shape[3] != D or not out.is_cuda):
+        raise KernelError(f"pw_attn_mma: q {tuple(q.shape)}, k pages {tuple(k_pages.shape)}, out {tuple(out.shape)} "
+                          f"strides {out.stride()}")
+    code = library().q3_pw_attn_mma(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), pk_pages.data_ptr(),
+                                    pv_pages.data_ptr(), out.data_ptr(), out.stride(0), ctx.q_start.data_ptr(),
+                                    ctx.kv_len.data_ptr(), table.data_ptr(), table.shape[1], k_pages.shape[0],
+                                    ptable.data_ptr(), ptable.shape[1], pk_pages.shape[0], k_pages.shape[2], ctx.num_seqs,
+                                    ctx.max_q_len, H, G, D, Dv, float(scale), float(softcap or 0.0), float(out_scale),
+                                    int(window), int(pool), status.data_ptr(), _stream())
+    _done("pw_attn_mma", code, f"heads {H}/{G}, dim {D}, vdim {Dv}")
+
+
 def pooled_window_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor,
                             pv_pages: torch.Tensor, ctx, table: torch.Tensor, ptable: torch.Tensor, out: torch.Tensor,
                             window: int, pool: int, scale: float, softcap: Optional[float], out_scale: float,
                             status: torch.Tensor) -> None:
-    """The attention of a step's batch over windows and pooled blocks, by the kernel that suits dtype and shape."""
-    pw_attn_ref(q, k_pages, v_pages, pk_pages, pv_pages, ctx.positions, ctx.tok_seq, table, ptable, out, window, pool,
-                scale, softcap, out_scale, status)
+    """The attention of a step's batch over windows and pooled blocks, by the kernel that suits dtype and shape: the
+    tensor-core kernel for bfloat16 heads it takes (an output whose rows and start allow paired stores), the plain
+    one for everything else."""
+    if (pw_attention_fast(q.dtype, q.shape[2], v_pages.shape[3]) and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
+        pw_attn_mma(q, k_pages, v_pages, pk_pages, pv_pages, ctx, table, ptable, out, window, pool, scale, softcap,
+                    out_scale, status)
+    else:
+        pw_attn_ref(q, k_pages, v_pages, pk_pages, pv_pages, ctx.positions, ctx.tok_seq, table, ptable, out, window, pool,
+                    scale, softcap, out_scale, status)
 
 
 # ------------------------------------------------------------------ a recurrence gated by the current token alone
+def mingru_chunk() -> int:
+    """Tokens per chunk of the chunked minGRU scan."""
+    if "mingru chunk" not in _DEVICE_FACTS:
+        _DEVICE_FACTS["mingru chunk"] = int(library()._lib.q3_mingru_chunk())
+    return _DEVICE_FACTS["mingru chunk"]
+
+
+def mingru_scratch_numel(num_tokens: int, num_seqs: int, channels: int) -> int:
+    """Floats of scratch that the chunked minGRU scan needs for a step of so many tokens and requests."""
+    return (num_tokens // mingru_chunk() + num_seqs + 1) * 2 * channels
+
+
+def mingru_chunked_pays(dtype: torch.dtype, max_q_len: int) -> bool:
+    """Whether a step whose longest portion has ``max_q_len`` tokens goes to the chunked scan: the bfloat16 run, from
+    four chunks on (the float32 run keeps the single walk, whose bits do not depend on the cut)."""
+    return dtype == torch.bfloat16 and max_q_len >= 4 * mingru_chunk()
+
+
 def mingru_scan(proj: torch.Tensor, z_col: int, u_col: int, g_col: int, z_bias: torch.Tensor, u_bias: torch.Tensor,
                 state: torch.Tensor, q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor,
-                out_scale: float, status: torch.Tensor) -> None:
+                out_scale: float, status: torch.Tensor, max_q_len: int = 0, scratch: Optional[torch.Tensor] = None) -> None:
     """z = sigmoid(proj[:, z_col..] + z_bias), u = proj[:, u_col..] + u_bias, candidate = u + 1/2 (u >= 0) or sigmoid(u);
     S <- (1 - z) S + z candidate per request, token by token (``state`` float32 [slots, C]);
-    out = S * silu(proj[:, g_col..]) * out_scale.  ``out``: [T, C], rows of any pitch."""
+    out = S * silu(proj[:, g_col..]) * out_scale.  ``out``: [T, C], rows of any pitch.  With ``scratch`` (float32,
+    ``mingru_scratch_numel``) and a longest portion ``max_q_len`` of ``mingru_chunked_pays`` the portions are cut
+    into chunks that run side by side."""
     _check("mingru_scan.proj", proj)
     _check("mingru_scan.state", state, torch.float32)
     for name, t in (("z_bias", z_bias), ("u_bias", u_bias)):
@@ -1846,6 +1916,17 @@ def mingru_scan(proj: torch.Tensor, z_col: int, u_col: int, g_col: int, z_bias: 
             or z_bias.numel() != C or u_bias.numel() != C or max(z_col, u_col, g_col) + C > ld or min(z_col, u_col, g_col) < 0):
         raise KernelError(f"mingru_scan: proj {tuple(proj.shape)}, columns {z_col}, {u_col}, {g_col}, state "
                           f"{tuple(state.shape)}, out {tuple(out.shape)}")
+    if scratch is not None and mingru_chunked_pays(proj.dtype, max_q_len):
+        _check("mingru_scan.scratch", scratch, torch.float32)
+        if scratch.numel() < mingru_scratch_numel(T, num_seqs, C):
+            raise KernelError(f"mingru_scan: scratch of {scratch.numel()} floats for {T} tokens of {num_seqs} requests")
+        code = library().q3_mingru_scan_chunked(
+            proj.data_ptr(), ld, int(z_col), int(u_col), int(g_col), z_bias.data_ptr(), u_bias.data_ptr(), state.data_ptr(),
+            scratch.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(), out.data_ptr(), out.stride(0),
+            dtype_tag(proj.dtype), T, int(num_seqs), int(max_q_len), C, state.shape[0], float(out_scale), status.data_ptr(),
+            _stream())
+        _done("mingru_scan_chunked", code, f"channels {C}")
+        return
     code = library().q3_mingru_scan(proj.data_ptr(), ld, int(z_col), int(u_col), int(g_col), z_bias.data_ptr(),
                                     u_bias.data_ptr(), state.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(),
                                     out.data_ptr(), out.stride(0), dtype_tag(proj.dtype), T, int(num_seqs), C, state.shape[0],
@@ -1903,7 +1984,80 @@ def moe_pairs(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.
     _done("moe_pairs", code, f"experts {E}, top {top}, inner {F}")
 
 
+MOE_GROUPED_FROM = 17  # tokens from which the sorted, grouped products run (below: a pair at a time)
+
+
+def moe_tile_rows() -> int:
+    """Rows per tile of the grouped products: every expert's rows start on a multiple of it."""
+    if "moe tile rows" not in _DEVICE_FACTS:
+        _DEVICE_FACTS["moe tile rows"] = int(library()._lib.q3_moe_tile_rows())
+    return _DEVICE_FACTS["moe tile rows"]
+
+
+def moe_grouped_tiles(num_tokens: int, top: int, experts: int) -> int:
+    """The most tiles that the sorted rows of so many tokens can fill: every expert wastes less than one."""
+    return (num_tokens * top) // moe_tile_rows() + experts
+
+
+def moe_grouped_takes(dtype: torch.dtype, width: int, ff: int) -> bool:
+    """Whether the grouped products take these experts: bfloat16, rows of whole 16-byte pieces."""
+    return dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0
+
+
+class MoeScratch:
+    """What the grouped products of at most ``max_tokens`` tokens keep between their kernels: the rows sorted by
+    expert (input, activations, output), every pair's row, every row's pair, and the list of tiles."""
+
+    def __init__(self, alloc, max_tokens: int, top: int, experts: int, width: int, ff: int):
+        rows = moe_grouped_tiles(max_tokens, top, experts) * moe_tile_rows()
+        self.sorted_in = alloc("moe.sorted_in", rows, width)
+        self.sorted_act = alloc("moe.sorted_act", rows, ff)
+        self.sorted_out = alloc("moe.sorted_out", rows, width)
+        self.pos = alloc("moe.pos", max_tokens * top, dtype=torch.int32)
+        self.src = alloc("moe.src", rows, dtype=torch.int32)
+        self.meta = alloc("moe.meta", 1 + rows // moe_tile_rows(), dtype=torch.int32)
+
+
+def moe_grouped(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                base: Optional[torch.Tensor], out: torch.Tensor, activation: str, scratch: MoeScratch,
+                status: torch.Tensor) -> None:
+    """out = base + sum_k weights[:, k] * down[ids[:, k]] act(up[ids[:, k]] h) for many tokens (bfloat16): the pairs
+    sorted by expert into whole tiles, both products of all experts as one grouped tensor-core product each."""
+    _check("moe_grouped.h", h, torch.bfloat16)
+    _check("moe_grouped.up", up, torch.bfloat16)
+    _check("moe_grouped.down", down, torch.bfloat16)
+    _check("moe_grouped.ids", ids, torch.int32)
+    _check("moe_grouped.weights", weights, torch.float32)
+    _check("moe_grouped.out", out, torch.bfloat16)
+    T, W = h.shape
+    E, F = up.shape[0], up.shape[1]
+    top = ids.shape[1]
+    tiles = moe_grouped_tiles(T, top, E)
+    rows = tiles * moe_tile_rows()
+    if base is not None:
+        _check("moe_grouped.base", base, torch.bfloat16)
+    if (tuple(up.shape) != (E, F, W) or tuple(down.shape) != (E, W, F) or tuple(ids.shape) != (T, top)
+            or tuple(weights.shape) != (T, top) or tuple(out.shape) != (T, W) or (base is not None and base.shape != h.shape)
+            or scratch.sorted_in.shape[0] < rows or scratch.sorted_in.shape[1] != W or scratch.sorted_act.shape[1] != F
+            or scratch.sorted_out.shape[1] != W or scratch.pos.numel() < T * top):
+        raise KernelError(f"moe_grouped: h {tuple(h.shape)}, up {tuple(up.shape)}, down {tuple(down.shape)}, ids "
+                          f"{tuple(ids.shape)}, out {tuple(out.shape)}, sorted rows {tuple(scratch.sorted_in.shape)}")
+    # the tensor maps cover the whole of the scratch rows, so that every step's maps are the same few
+    cap = scratch.sorted_in.shape[0] // moe_tile_rows()
+    code = library().q3_moe_grouped(h.data_ptr(), up.data_ptr(), down.data_ptr(), ids.data_ptr(), weights.data_ptr(),
+                                    _ptr(base), out.data_ptr(), scratch.sorted_in.data_ptr(), scratch.sorted_act.data_ptr(),
+                                    scratch.sorted_out.data_ptr(), scratch.pos.data_ptr(), scratch.src.data_ptr(),
+                                    scratch.meta.data_ptr(), T, W, F, E, top, cap, activation_code(activation, gate=True),
+                                    status.data_ptr(), _stream())
+    _done("moe_grouped", code, f"experts {E}, top {top}, width {W}, ff {F}")
+
+
 def routed_experts(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                   base: Optional[torch.Tensor], act_buf: torch.Tensor, out: torch.Tensor, activation: str) -> None:
-    """The chosen experts of a step's tokens, by the kernels that suit dtype and shape (see ``moe_pairs``)."""
-    moe_pairs(h, up, down, ids, weights, base, act_buf, out, activation)
+                   base: Optional[torch.Tensor], act_buf: torch.Tensor, out: torch.Tensor, activation: str,
+                   scratch: Optional[MoeScratch] = None, status: Optional[torch.Tensor] = None) -> None:
+    """The chosen experts of a step's tokens, by the kernels that suit dtype and shape: with ``scratch``, from
+    ``MOE_GROUPED_FROM`` tokens on, the grouped tensor-core products; otherwise a pair at a time (``moe_pairs``)."""
+    if scratch is not None and status is not None and h.shape[0] >= MOE_GROUPED_FROM:
+        moe_grouped(h, up, down, ids, weights, base, out, activation, scratch, status)
+    else:
+        moe_pairs(h, up, down, ids, weights, base, act_buf, out, activation)

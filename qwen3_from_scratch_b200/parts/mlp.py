@@ -194,6 +194,10 @@ class RoutedExperts(FeedForward):
         self._weights = rt.shared("moe.weights", T, self.top, dtype=torch.float32)
         self._act = rt.shared("moe.act", T * self.top, self.expert_ff)
         self._out = rt.shared("moe.out", T, self.hidden_size)
+        self._status = rt.status
+        self._grouped = None
+        if ops.moe_grouped_takes(rt.dtype, self.hidden_size, self.expert_ff):
+            self._grouped = ops.MoeScratch(rt.shared, T, self.top, self.experts, self.hidden_size, self.expert_ff)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
@@ -201,5 +205,6 @@ class RoutedExperts(FeedForward):
         ops.moe_route(x, self.router, self.correction, ids, wts, self.router_scale)
         base = self.shared.forward(x) if self.shared is not None else None
         out = self._out[:T]
-        ops.routed_experts(x, self.up, self.down, ids, wts, base, self._act[: T * self.top], out, self.activation)
+        ops.routed_experts(x, self.up, self.down, ids, wts, base, self._act[: T * self.top], out, self.activation,
+                           scratch=self._grouped, status=self._status)
         return out

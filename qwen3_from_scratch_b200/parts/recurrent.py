@@ -303,6 +303,10 @@ class MinGRU(Mixer, _NamedTensors):
     def setup_core(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         self.rt = rt
         self.z_bias, self.x_bias = weights[self.tensors["z_bias"]], weights[self.tensors["x_bias"]]
+        self._chunks = None
+        if rt.dtype == torch.bfloat16:
+            self._chunks = rt.shared("mingru.chunks", ops.mingru_scratch_numel(rt.max_tokens, rt.max_seqs, self.width),
+                                     dtype=torch.float32)
 
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
@@ -315,7 +319,8 @@ class MinGRU(Mixer, _NamedTensors):
              out: torch.Tensor, out_scale: float) -> None:
         c = self.width
         ops.mingru_scan(proj, column, column + c, column + 2 * c, self.z_bias, self.x_bias, ctx.state(cache_id),
-                        ctx.q_start, ctx.slot_ids, ctx.num_seqs, out, out_scale, self.rt.status)
+                        ctx.q_start, ctx.slot_ids, ctx.num_seqs, out, out_scale, self.rt.status, max_q_len=ctx.max_q_len,
+                        scratch=self._chunks)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         gated = self._gated[: x.shape[0]]

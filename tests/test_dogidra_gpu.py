@@ -231,6 +231,56 @@ def test_routed_experts_few_rows_and_many(E, top, ff, shared, rows, dtype):
     close(got[sure], want[sure], dtype, f"{rows} rows")
 
 
+@pytest.mark.parametrize("W,E,top,ff,shared,rows", [(320, 8, 2, 264, 72, 900), (136, 3, 3, 520, None, 1500),
+                                                     (64, 40, 5, 8, 16, 333)])
+def test_routed_experts_grouped_products_over_several_tiles(W, E, top, ff, shared, rows):
+    """bfloat16 and many rows: the sorted, grouped products with several tiles per expert, several tiles of columns, an
+    inner size that is no multiple of a tile's 64, more experts than rows per tile; then a few rows through the same
+    part (a pair at a time) while the sorted rows still hold the step before."""
+    from qwen3_from_scratch_b200.parts.base import PartSpec, Runtime
+    from qwen3_from_scratch_b200.registry import create_part
+    sh = None if shared is None else PartSpec("dense_mlp", {"hidden_size": W, "intermediate_size": shared,
+                                                            "activation": "relu_sq", "names": {"up": "up", "down": "down"}})
+    part = create_part("feed_forward", PartSpec("routed_experts", {
+        "hidden_size": W, "experts": E, "top": top, "expert_ff": ff, "router_scale": 0.8, "activation": "relu_sq",
+        "shared": sh}), name="f")
+    dev, ref = part_weights(part, "bfloat16", seed=rows, scale={"router": 6.0})
+    rt = Runtime(torch.device("cuda:0"), torch.bfloat16, 2048, 2)
+    part.setup(rt, dict(dev))
+    mlp = {"router": {"experts": E, "top": top, "scale": 0.8}, "expert": {"ff": ff}, "shared": {"ff": shared} if shared else None}
+    for n, seed in ((rows, 1), (rows // 3, 2), (5, 3), (rows, 1)):
+        x = torch.randn(n, W, generator=torch.Generator().manual_seed(rows + seed)).to(torch.bfloat16)
+        want = plain.routed_experts(x.double(), ref, "", mlp)
+        got = part.forward(x.cuda()).double().cpu()
+        s = plain.sigmoid(x.double() @ ref["router"].t()) + ref["correction"]
+        order = torch.sort(s, dim=-1, descending=True).values
+        sure = (order[:, top - 1] - order[:, top] > 1e-3) if top < E else torch.ones(n, dtype=torch.bool)
+        assert int(sure.sum()) >= int(n * 0.9)
+        close(got[sure], want[sure], "bfloat16", f"{n} rows")
+    assert int(rt.status.item()) == 0
+
+
+def test_chunked_recurrence_of_long_portions_side_by_side():
+    """bfloat16: two requests with portions long enough for the chunked scan in one step (lengths that are no multiple
+    of a chunk), after a first portion each that left a state, and single tokens after; a width that fills no warp."""
+    from qwen3_from_scratch_b200.parts.base import PartSpec
+    from qwen3_from_scratch_b200.registry import create_part
+    params = {"hidden_size": 32, "width": 37}
+    part = create_part("mixer", PartSpec("mingru", params), name="m")
+    bench = MixerBench(part, "bfloat16", page_size=8, pages=8, max_tokens=1024, seed=61)
+    g = torch.Generator().manual_seed(62)
+    x_of = {"a": torch.randn(420, 32, generator=g).to(torch.bfloat16), "b": torch.randn(391, 32, generator=g).to(torch.bfloat16)}
+    fn = _mingru(params)
+    want = {r: fn(x.double(), bench.ref, None)[0] for r, x in x_of.items()}
+    call = lambda rows, ctx: part.forward(rows.cuda().contiguous(), ctx, 0, True)  # noqa: E731
+    got = {r: [] for r in x_of}
+    for step in ([("a", 3)], [("b", 70), ("a", 1)], [("a", 301), ("b", 257)], [("b", 1), ("a", 1)], [("a", 114), ("b", 63)]):
+        for r, y in bench.run(step, x_of, call).items():
+            got[r].append(y)
+    for r in x_of:
+        close(torch.cat(got[r]), want[r], "bfloat16", f"request {r}")
+
+
 def _sharp_scores(x, ref, params):
     """(largest softmax weight [heads, n], what holds it: a token's distance back, or -1 - b for block b)."""
     n, H, G, D = x.shape[0], params["num_heads"], params["num_kv_heads"], params["dim"]
@@ -278,7 +328,7 @@ def test_sharp_attention_reads_the_windows_edges_and_far_blocks(dtype):
     assert int((what[sharp] == 0).sum()) > 3, "the query's own key"
     assert int(((-1 - what == newest_block) & sharp).sum()) > 3, "the block that has just become visible"
     assert int(((what == -1) & sharp & (pos > 200)).sum()) > 0, "the first block from far away"
-    assert int(((what < 0) & sharp & (newest_block + 1 + what > 60)).sum()) > 10, "blocks far back"
+    assert int(((what < 0) & sharp & (newest_block + 1 + what > 60)).sum()) > 3, "blocks far back"
     rows = sharp.all(0).nonzero()[:, 0] if dtype == "bfloat16" else torch.arange(n)
     assert rows.numel() > 40
     call = lambda r, ctx: part.forward(r.cuda().contiguous(), ctx, 0, True)  # noqa: E731
