@@ -17,6 +17,17 @@ namespace q3 {
 
 constexpr int MOE_MAX_TOP = 32;
 
+__device__ __forceinline__ void load4(const float* p, float (&x)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  x[0] = v.x, x[1] = v.y, x[2] = v.z, x[3] = v.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&x)[4]) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  x[0] = a.x, x[1] = a.y, x[2] = b.x, x[3] = b.y;
+}
+
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ bias,
                                  int* __restrict__ ids, float* __restrict__ wts, int W, int E, int top, float scale) {
@@ -26,10 +37,25 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const T* row = h + (size_t)t * W;
+  // four values per lane and turn where the rows allow it, so that a warp has its loads in flight together
+  const bool by4 = (W & 3) == 0 && ((uintptr_t)row & (4 * sizeof(T) - 1)) == 0 && ((uintptr_t)wr & 15) == 0;
   for (int e = warp; e < E; e += nwarps) {
     const float* w = wr + (size_t)e * W;
     float dot = 0.f;
-    for (int i = lane; i < W; i += 32) dot = fmaf(to_float(row[i]), w[i], dot);
+    if (by4) {
+#pragma unroll 4
+      for (int i = 4 * lane; i < W; i += 128) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + i);
+        float x[4];
+        load4(row + i, x);
+        dot = fmaf(x[0], wv.x, dot);
+        dot = fmaf(x[1], wv.y, dot);
+        dot = fmaf(x[2], wv.z, dot);
+        dot = fmaf(x[3], wv.w, dot);
+      }
+    } else {
+      for (int i = lane; i < W; i += 32) dot = fmaf(to_float(row[i]), w[i], dot);
+    }
     dot = warp_sum(dot);
     if (lane == 0) {
       const float s = 1.0f / (1.0f + expf(-dot));
@@ -115,7 +141,8 @@ extern "C" int q3_moe_route(const void* h, const float* wr, const float* bias, i
                             int E, int top, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (W <= 0 || E <= 0 || top <= 0 || top > E || top > q3::MOE_MAX_TOP || E > 4096) return Q3_ERR_SIZE;
-  Q3_BY_DTYPE(dtype, q3::launch(q3::moe_route_kernel<E_>, dim3(T), dim3(128), (size_t)2 * E * sizeof(float), stream,
+  Q3_BY_DTYPE(dtype, q3::launch(q3::moe_route_kernel<E_>, dim3(T), dim3(E >= 8 ? 256 : 128), (size_t)2 * E * sizeof(float),
+                                stream,
                                 (const E_*)h, wr, bias, ids, wts, W, E, top, scale))
   return q3::launch_status();
 }

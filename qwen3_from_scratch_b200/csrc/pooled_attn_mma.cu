@@ -8,6 +8,11 @@
 // (cp.async, two stages).  S = Q K^T and O += P V run on m16n8k16 (bfloat16 in, float32 accumulate); scale, cap,
 // masks, running maximum, denominator and output are float32.  A row at position p with lo = max(0, p - window + 1)
 // reads the tokens lo .. p and the blocks 0 .. lo / P - 1.  Keys and values have sizes of their own (D, Dv).
+//
+// A step of single tokens has one query tile per (kv head, sequence), too few blocks for the GPU: the tile list is
+// then cut into `splits` equal ranges, one block each, which leave their running maximum, denominator and
+// unnormalised output in scratch; pw_attn_merge_kernel adds the ranges up in ascending order.  How many ranges
+// there are depends on the batch's size alone, so a captured step replays the same launches.
 #include "attn_mma.cuh"
 
 namespace q3 {
@@ -36,7 +41,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ q_start, const int* __restrict__ kv_len, const int* __restrict__ block_table,
                    int table_stride, int num_pages, const int* __restrict__ pooled_table, int ptable_stride,
                    int num_ppages, int page_size, int Hq, int Hkv, float scale, float cap, float out_scale, int window,
-                   int P, int* status) {
+                   int P, int splits, int T_total, float* __restrict__ part_o, float* __restrict__ part_ml, int* status) {
   pdl_wait();
   pdl_launch_dependents();
   using S = PwShape<KT, VT>;
@@ -49,7 +54,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tid4 = lane & 3;
-  const int qt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int qt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z / splits, sp = blockIdx.z - b * splits;
   const int g = Hq / Hkv;
   const int qs = q_start[b];
   const int q_len = q_start[b + 1] - qs;
@@ -71,6 +76,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int ptiles = (blocks_hi + PWM_BN - 1) / PWM_BN;
   const int tile_lo = lo_key / PWM_BN, tile_hi = pos_last / PWM_BN;
   const int tiles = ptiles + tile_hi - tile_lo + 1;
+  const int vt_begin = (int)((long long)tiles * sp / splits), vt_end = (int)((long long)tiles * (sp + 1) / splits);
 
   for (int e = threadIdx.x; e < BM * KCPR; e += WARPS * 32) {
     const int rr = e / KCPR, c = e % KCPR;
@@ -108,7 +114,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     for (int c = part; c < VCPR; c += LANES_PER_ROW) cp_async_16(vd + c * 8, vs + (bytes ? c * 8 : 0), bytes);
   };
 
-  load_tile(0, 0);
+  if (vt_begin < vt_end) load_tile(vt_begin, 0);
   cp_async_commit();
   __syncthreads();  // the query tile is in place
 
@@ -130,9 +136,9 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
   constexpr float LOG2E = 1.4426950408889634f;
 
-  for (int vt = 0; vt < tiles; ++vt) {
-    const int stage = vt & 1;
-    if (vt + 1 < tiles) load_tile(vt + 1, stage ^ 1);
+  for (int vt = vt_begin; vt < vt_end; ++vt) {
+    const int stage = (vt - vt_begin) & 1;
+    if (vt + 1 < vt_end) load_tile(vt + 1, stage ^ 1);
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();
@@ -218,6 +224,17 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
     const int R = row0 + warp * 16 + gid + 8 * r;
     if (R >= total_rows) continue;
+    if (splits > 1) {  // this range's share: maximum (base-2 units), denominator, unnormalised output
+      const size_t row = ((size_t)sp * T_total + qs + R / g) * Hq + hk * g + R % g;
+      if (tid4 == 0) {
+        part_ml[2 * row] = m[r];
+        part_ml[2 * row + 1] = l[r];
+      }
+      float* dst = part_o + row * DV + 2 * tid4;
+#pragma unroll
+      for (int nt = 0; nt < 2 * VT; ++nt) *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][2 * r], o[nt][2 * r + 1]);
+      continue;
+    }
     const float inv = l[r] > 0.f ? out_scale / l[r] : 0.f;
     __nv_bfloat16* dst = out + (size_t)(qs + R / g) * ldo + (size_t)(hk * g + R % g) * DV + 2 * tid4;
 #pragma unroll
@@ -226,12 +243,36 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
 }
 
+// grid (tokens, heads), a thread per output value: the ranges' shares in ascending order.
+__global__ void pw_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                     __nv_bfloat16* __restrict__ out, int ldo, int T_total, int Hq, int DV, int splits,
+                                     float out_scale) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, h = blockIdx.y;
+  float mx = -INFINITY;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[2 * (((size_t)s * T_total + t) * Hq + h)]);
+  for (int d = threadIdx.x; d < DV; d += blockDim.x) {
+    float acc = 0.f, den = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const size_t row = ((size_t)s * T_total + t) * Hq + h;
+      const float ms = part_ml[2 * row];
+      if (ms == -INFINITY) continue;
+      const float w = exp2f(ms - mx);
+      den = fmaf(w, part_ml[2 * row + 1], den);
+      acc = fmaf(w, part_o[row * DV + d], acc);
+    }
+    out[(size_t)t * ldo + (size_t)h * DV + d] = __float2bfloat16_rn(den > 0.f ? acc * (out_scale / den) : 0.f);
+  }
+}
+
 template <int KT, int VT>
 static int pw_attn_mma_launch(const void* q, const void* k_pages, const void* v_pages, const void* pk_pages,
                               const void* pv_pages, void* out, int ldo, const int* q_start, const int* kv_len,
                               const int* table, int stride, int num_pages, const int* ptable, int pstride, int num_ppages,
                               int page_size, int B, int max_q_len, int Hq, int Hkv, float scale, float cap, float out_scale,
-                              int window, int P, int* status, cudaStream_t stream) {
+                              int window, int P, int T_total, float* part_o, float* part_ml, long long part_rows,
+                              int* status, cudaStream_t stream) {
   using S = PwShape<KT, VT>;
   static bool configured = false;
   if (!configured) {
@@ -243,10 +284,24 @@ static int pw_attn_mma_launch(const void* q, const void* k_pages, const void* v_
   const int g = Hq / Hkv;
   const long long tiles = ((long long)max_q_len * g + S::BM - 1) / S::BM;
   if (tiles > 0x7fffffffLL) return Q3_ERR_SIZE;
-  q3::launch(pw_attn_mma_kernel<KT, VT>, dim3((unsigned)tiles, Hkv, B), dim3(S::WARPS * 32), S::SMEM_BYTES, stream,
+  // one query tile per (kv head, sequence): ranges of the keys until two blocks per SM are there, as far as the
+  // scratch goes
+  int splits = 1;
+  if (tiles == 1 && part_o && part_ml && T_total > 0) {
+    const long long blocks = (long long)Hkv * B, room = part_rows / ((long long)T_total * Hq);
+    long long want = (2LL * sm_count() + blocks - 1) / blocks;
+    want = want < room ? want : room;
+    splits = (int)(want < 1 ? 1 : (want > 32 ? 32 : want));
+    if ((long long)B * splits > 65535) splits = 1;
+  }
+  q3::launch(pw_attn_mma_kernel<KT, VT>, dim3((unsigned)tiles, Hkv, B * splits), dim3(S::WARPS * 32), S::SMEM_BYTES, stream,
              (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
              (const __nv_bfloat16*)pk_pages, (const __nv_bfloat16*)pv_pages, (__nv_bfloat16*)out, ldo, q_start, kv_len, table,
-             stride, num_pages, ptable, pstride, num_ppages, page_size, Hq, Hkv, scale, cap, out_scale, window, P, status);
+             stride, num_pages, ptable, pstride, num_ppages, page_size, Hq, Hkv, scale, cap, out_scale, window, P, splits,
+             T_total, part_o, part_ml, status);
+  if (splits > 1)
+    q3::launch(pw_attn_merge_kernel, dim3(T_total, Hq), dim3(S::DV < 128 ? S::DV : 128), 0, stream, (const float*)part_o,
+               (const float*)part_ml, (__nv_bfloat16*)out, ldo, T_total, Hq, S::DV, splits, out_scale);
   return launch_status();
 }
 
@@ -259,12 +314,15 @@ extern "C" int q3_pw_attn_mma_takes(int D, int Dv) {
 }
 
 // q: bf16 [T, Hq, D]; token pages k [pages, Hkv, page, D], v [.., Dv]; block pages pk, pv alike; out: rows of `ldo`
-// values, head h at column h * Dv, times out_scale.  cap <= 0: no cap.
+// values, head h at column h * Dv, times out_scale.  cap <= 0: no cap.  part_o (float32, part_rows * Dv values) and part_ml
+// (float32, part_rows * 2 values), or null: scratch for a step of T tokens whose keys are cut into ranges (part_rows /
+// (T * Hq) of them at most).
 extern "C" int q3_pw_attn_mma(const void* q, const void* k_pages, const void* v_pages, const void* pk_pages,
                               const void* pv_pages, void* out, int ldo, const int* q_start, const int* kv_len,
                               const int* table, int stride, int num_pages, const int* ptable, int pstride, int num_ppages,
                               int page_size, int B, int max_q_len, int Hq, int Hkv, int D, int Dv, float scale, float cap,
-                              float out_scale, int window, int P, int* status, cudaStream_t stream) {
+                              float out_scale, int window, int P, int T, float* part_o, float* part_ml, long long part_rows,
+                              int* status, cudaStream_t stream) {
   if (B <= 0 || max_q_len <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv || !q3_pw_attn_mma_takes(D, Dv) || page_size <= 0 || stride <= 0 || pstride <= 0 || B > 65535 ||
       Hkv > 65535 || window <= 0 || P <= 0 || ldo % 2)
@@ -276,7 +334,8 @@ extern "C" int q3_pw_attn_mma(const void* q, const void* k_pages, const void* v_
   if (D == 16 * KT && Dv == 16 * VT)                                                                                    \
     return q3::pw_attn_mma_launch<KT, VT>(q, k_pages, v_pages, pk_pages, pv_pages, out, ldo, q_start, kv_len, table,    \
                                           stride, num_pages, ptable, pstride, num_ppages, page_size, B, max_q_len, Hq,  \
-                                          Hkv, scale, cap, out_scale, window, P, status, stream);
+                                          Hkv, scale, cap, out_scale, window, P, T, part_o, part_ml, part_rows, status,   \
+                                          stream);
   Q3_PW_CASE(2, 2) Q3_PW_CASE(2, 4) Q3_PW_CASE(2, 8) Q3_PW_CASE(4, 2) Q3_PW_CASE(4, 4) Q3_PW_CASE(4, 8) Q3_PW_CASE(8, 2)
   Q3_PW_CASE(8, 4) Q3_PW_CASE(8, 8)
 #undef Q3_PW_CASE

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -157,7 +157,8 @@ _SIGNATURES = {
                        _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void_p, _c_void_p],
     "q3_pw_attn_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                       _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
+                       _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_ll,
+                       _c_void_p, _c_void_p],
     "q3_mingru_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "q3_moe_grouped": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
@@ -1840,9 +1841,12 @@ def pw_attention_fast(dtype: torch.dtype, dim: int, vdim: int) -> bool:
 
 def pw_attn_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor,
                 pv_pages: torch.Tensor, ctx, table: torch.Tensor, ptable: torch.Tensor, out: torch.Tensor, window: int,
-                pool: int, scale: float, softcap: Optional[float], out_scale: float, status: torch.Tensor) -> None:
+                pool: int, scale: float, softcap: Optional[float], out_scale: float, status: torch.Tensor,
+                partial: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
     """The same attention as ``pw_attn_ref`` on the tensor cores (bfloat16): tiles of 64 entries of the block pages
-    and of the token pages in one online softmax, 128 (token, head) rows of one kv head to a block."""
+    and of the token pages in one online softmax, 128 (token, head) rows of one kv head to a block.  ``partial``
+    (``pw_attn_partial``): scratch with which a step of single tokens cuts every request's keys into ranges that run
+    side by side and are merged in ascending order."""
     _check("pw_attn_mma.q", q, torch.bfloat16)
     _pw_pages("pw_attn_mma", k_pages, v_pages, pk_pages, pv_pages, q.dtype)
     for name, t in (("q_start", ctx.q_start), ("kv_len", ctx.kv_len), ("table", table), ("ptable", ptable)):
@@ -1853,25 +1857,44 @@ def pw_attn_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, p
             or k_pages.shape[3] != D or not out.is_cuda):
         raise KernelError(f"pw_attn_mma: q {tuple(q.shape)}, k pages {tuple(k_pages.shape)}, out {tuple(out.shape)} "
                           f"strides {out.stride()}")
+    part_o = part_ml = None
+    part_rows = 0
+    if partial is not None:
+        part_o, part_ml = partial
+        _check("pw_attn_mma.partial", part_o, torch.float32)
+        _check("pw_attn_mma.partial", part_ml, torch.float32)
+        part_rows = min(part_o.numel() // Dv, part_ml.numel() // 2)
     code = library().q3_pw_attn_mma(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), pk_pages.data_ptr(),
                                     pv_pages.data_ptr(), out.data_ptr(), out.stride(0), ctx.q_start.data_ptr(),
                                     ctx.kv_len.data_ptr(), table.data_ptr(), table.shape[1], k_pages.shape[0],
                                     ptable.data_ptr(), ptable.shape[1], pk_pages.shape[0], k_pages.shape[2], ctx.num_seqs,
                                     ctx.max_q_len, H, G, D, Dv, float(scale), float(softcap or 0.0), float(out_scale),
-                                    int(window), int(pool), status.data_ptr(), _stream())
+                                    int(window), int(pool), T, _ptr(part_o), _ptr(part_ml), part_rows, status.data_ptr(),
+                                    _stream())
     _done("pw_attn_mma", code, f"heads {H}/{G}, dim {D}, vdim {Dv}")
+
+
+PW_ATTN_MAX_RANGES = 32  # the most ranges that the keys of a request are cut into
+
+
+def pw_attn_partial(alloc, max_seqs: int, heads: int, vdim: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Scratch for ``pw_attn_mma``: room for the most ranges for a step of ``max_seqs`` single tokens (a step of more
+    tokens gets fewer ranges)."""
+    rows = max_seqs * heads * PW_ATTN_MAX_RANGES
+    return (alloc("pwattn.partial_o", rows * vdim, dtype=torch.float32),
+            alloc("pwattn.partial_ml", rows * 2, dtype=torch.float32))
 
 
 def pooled_window_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor,
                             pv_pages: torch.Tensor, ctx, table: torch.Tensor, ptable: torch.Tensor, out: torch.Tensor,
                             window: int, pool: int, scale: float, softcap: Optional[float], out_scale: float,
-                            status: torch.Tensor) -> None:
+                            status: torch.Tensor, partial: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
     """The attention of a step's batch over windows and pooled blocks, by the kernel that suits dtype and shape: the
     tensor-core kernel for bfloat16 heads it takes (an output whose rows and start allow paired stores), the plain
     one for everything else."""
     if (pw_attention_fast(q.dtype, q.shape[2], v_pages.shape[3]) and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
         pw_attn_mma(q, k_pages, v_pages, pk_pages, pv_pages, ctx, table, ptable, out, window, pool, scale, softcap,
-                    out_scale, status)
+                    out_scale, status, partial)
     else:
         pw_attn_ref(q, k_pages, v_pages, pk_pages, pv_pages, ctx.positions, ctx.tok_seq, table, ptable, out, window, pool,
                     scale, softcap, out_scale, status)

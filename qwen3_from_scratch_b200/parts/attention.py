@@ -413,6 +413,9 @@ class PooledWindowAttention(Mixer):
         self.q_norm, self.k_norm = weights[self.tensors["q_norm"]], weights[self.tensors["k_norm"]]
         self.position.setup(rt, weights)
         self._q = rt.shared("pwattn.q", rt.max_tokens, self.num_heads, self.dim)
+        self._partial = None
+        if ops.pw_attention_fast(rt.dtype, self.dim, self.vdim):
+            self._partial = ops.pw_attn_partial(rt.shared, rt.max_seqs, self.num_heads, self.vdim)
 
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
@@ -436,7 +439,7 @@ class PooledWindowAttention(Mixer):
             ops.pool_blocks(planes["k"], planes["v"], pooled["pk"], pooled["pv"], ctx.q_start, ctx.kv_len, table, ptable,
                             ctx.num_seqs, ctx.max_q_len, self.pool, status)
         ops.pooled_window_attention(q, planes["k"], planes["v"], pooled["pk"], pooled["pv"], ctx, table, ptable, out,
-                                    self.window, self.pool, self.scale, self.softcap, out_scale, status)
+                                    self.window, self.pool, self.scale, self.softcap, out_scale, status, self._partial)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         o = self._o[: x.shape[0]]

@@ -167,6 +167,10 @@ def mixers():
                                                        position=rot(0, 10000.0)),
         # seventeen query heads on one key head (more than a tensor-core tile's sixteen rows), a page's worth of window
         "pooled_window_attention, many heads": dict(att, num_heads=17, num_kv_heads=1, dim=16, vdim=16, window=16, pool=5),
+        # sizes that the tensor-core kernel takes: steps of single tokens cut the keys into ranges, most of them empty
+        "pooled_window_attention, tensor cores": dict(att, num_heads=4, num_kv_heads=2, dim=32, vdim=64),
+        "pooled_window_attention, tensor cores, wide heads": dict(att, num_heads=3, num_kv_heads=1, dim=128, vdim=32,
+                                                                  window=5, pool=2, softcap=None),
         "mingru": {"hidden_size": 40, "width": 72},
         "mingru, odd": {"hidden_size": 40, "width": 37},
     }
@@ -178,7 +182,8 @@ def mixers():
 
 
 MIXER_KINDS = ["pooled_window_attention", "pooled_window_attention, long blocks", "pooled_window_attention, blocks of one",
-               "pooled_window_attention, many heads", "mingru", "mingru, odd", "parallel"]
+               "pooled_window_attention, many heads", "pooled_window_attention, tensor cores",
+               "pooled_window_attention, tensor cores, wide heads", "mingru", "mingru, odd", "parallel"]
 
 
 @pytest.mark.parametrize("dtype", list(DT))
@@ -303,7 +308,8 @@ def _sharp_scores(x, ref, params):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
-def test_sharp_attention_reads_the_windows_edges_and_far_blocks(dtype):
+@pytest.mark.parametrize("dim,vdim", [(16, 24), (32, 64)])  # the second: sizes that the tensor-core kernel takes
+def test_sharp_attention_reads_the_windows_edges_and_far_blocks(dim, vdim, dtype):
     """A scale so large that nearly every query gives all its weight to one key or one block, which random weights
     put anywhere: the window's oldest token, the query's own, the block that has just become visible, blocks
     hundreds of tokens back, the very first block, slots at a page's border.  A key that is lost, read one token
@@ -312,7 +318,7 @@ def test_sharp_attention_reads_the_windows_edges_and_far_blocks(dtype):
     from qwen3_from_scratch_b200.parts.base import PartSpec
     from qwen3_from_scratch_b200.registry import create_part
     W, n, page = 32, 330, 8
-    params = {"hidden_size": W, "num_heads": 4, "num_kv_heads": 2, "dim": 16, "vdim": 24, "scale": 7.0, "softcap": None,
+    params = {"hidden_size": W, "num_heads": 4, "num_kv_heads": 2, "dim": dim, "vdim": vdim, "scale": 7.0, "softcap": None,
               "window": 11, "pool": 3, "norm_eps": 1e-5,
               "position": PartSpec("rotary_stretched", {"dims": 8, "base": 10000.0, "scaling": None})}
     part = create_part("mixer", PartSpec("pooled_window_attention", params), name="m")
