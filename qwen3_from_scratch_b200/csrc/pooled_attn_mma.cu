@@ -19,22 +19,25 @@ namespace q3 {
 
 constexpr int PWM_BN = 64;  // entries per tile
 
-template <int KT, int VT>
+// DEC: a step whose requests bring at most 16 (token, head) rows per kv head (single tokens): one row group of 16 to
+// a block, and the block's four warps take a quarter of every tile's 64 entries each, with a running maximum,
+// denominator and output of their own, which meet in shared memory at the end.
+template <int KT, int VT, bool DEC = false>
 struct PwShape {
   static constexpr int D = 16 * KT, DV = 16 * VT;
   static constexpr int KPITCH = D + 8, VPITCH = DV + 8;
   static constexpr int KTILE = PWM_BN * KPITCH, VTILE = PWM_BN * VPITCH;
-  static constexpr int WARPS = (KT <= 8 && VT <= 8) ? 8 : 4;
-  static constexpr int BM = 16 * WARPS;
-  static constexpr int MIN_BLOCKS = (KT <= 8 && VT <= 8) ? 2 : 1;
+  static constexpr int WARPS = DEC ? 4 : ((KT <= 8 && VT <= 8) ? 8 : 4);
+  static constexpr int BM = DEC ? 16 : 16 * WARPS;
+  static constexpr int MIN_BLOCKS = DEC ? 3 : ((KT <= 8 && VT <= 8) ? 2 : 1);
   static constexpr size_t SMEM_BYTES = sizeof(__nv_bfloat16) * (size_t)(BM * KPITCH + 2 * (KTILE + VTILE));
 };
 
 // tanh through one exponential: 1 - 2 / (e^(2x) + 1); absolute error of a few 1e-7, both tails exact
 __device__ __forceinline__ float pw_tanh(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
 
-template <int KT, int VT>
-__global__ void __launch_bounds__(PwShape<KT, VT>::WARPS * 32, PwShape<KT, VT>::MIN_BLOCKS)
+template <int KT, int VT, bool DEC>
+__global__ void __launch_bounds__(PwShape<KT, VT, DEC>::WARPS * 32, PwShape<KT, VT, DEC>::MIN_BLOCKS)
 pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pages,
                    const __nv_bfloat16* __restrict__ v_pages, const __nv_bfloat16* __restrict__ pk_pages,
                    const __nv_bfloat16* __restrict__ pv_pages, __nv_bfloat16* __restrict__ out, int ldo,
@@ -44,7 +47,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    int P, int splits, int T_total, float* __restrict__ part_o, float* __restrict__ part_ml, int* status) {
   pdl_wait();
   pdl_launch_dependents();
-  using S = PwShape<KT, VT>;
+  using S = PwShape<KT, VT, DEC>;
   constexpr int D = S::D, DV = S::DV, KPITCH = S::KPITCH, VPITCH = S::VPITCH, KCPR = D / 8, VCPR = DV / 8;
   constexpr int WARPS = S::WARPS, BM = S::BM;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -54,6 +57,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gid = lane >> 2, tid4 = lane & 3;
+  const int wrow = DEC ? 0 : warp * 16;  // the warp's first row of the block's rows
   const int qt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z / splits, sp = blockIdx.z - b * splits;
   const int g = Hq / Hkv;
   const int qs = q_start[b];
@@ -118,12 +122,12 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   cp_async_commit();
   __syncthreads();  // the query tile is in place
 
-  const __nv_bfloat16* q_warp = q_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * KPITCH + (lane >> 4) * 8;
+  const __nv_bfloat16* q_warp = q_s + (wrow + (lane & 7) + ((lane >> 3) & 1) * 8) * KPITCH + (lane >> 4) * 8;
 
   int row_pos[2], row_lo[2], row_blocks[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    const int R = row0 + warp * 16 + gid + 8 * r;
+    const int R = row0 + wrow + gid + 8 * r;
     row_pos[r] = R < total_rows ? past + R / g : pos_last;  // rows past the end compute something finite, unused
     row_lo[r] = max(0, row_pos[r] - window + 1);
     row_blocks[r] = row_lo[r] / P;
@@ -154,6 +158,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       ldmatrix_x4(qf, q_warp + kt * 16);
 #pragma unroll
       for (int np = 0; np < 4; ++np) {
+        if (DEC && np != warp) continue;  // this warp's sixteen entries of the tile
         uint32_t kb[4];
         ldmatrix_x4(kb, kt_s + (np * 16 + (lane & 7) + ((lane >> 4) << 3)) * KPITCH + kt * 16 + ((lane >> 3) & 1) * 8);
         mma_bf16(s[2 * np], qf, kb[0], kb[1]);
@@ -166,6 +171,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
+        if (DEC && (nt >> 1) != warp) continue;
         const int n = base_n + nt * 8 + 2 * tid4 + (j & 1);
         float v = s[nt][j] * scale;
         if (cap > 0.f) v = cap * pw_tanh(v * inv_cap);
@@ -178,7 +184,8 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     for (int r = 0; r < 2; ++r) {
       float mx = -INFINITY;
 #pragma unroll
-      for (int nt = 0; nt < 8; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * r], s[nt][2 * r + 1]));
+      for (int nt = 0; nt < 8; ++nt)
+        if (!DEC || (nt >> 1) == warp) mx = fmaxf(mx, fmaxf(s[nt][2 * r], s[nt][2 * r + 1]));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_new = fmaxf(m[r], mx);
@@ -193,6 +200,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       }
 #pragma unroll
       for (int nt = 0; nt < 8; ++nt) {
+        if (DEC && (nt >> 1) != warp) continue;
         const float p0 = exp2f(s[nt][2 * r] - m_use), p1 = exp2f(s[nt][2 * r + 1] - m_use);
         s[nt][2 * r] = p0;
         s[nt][2 * r + 1] = p1;
@@ -201,6 +209,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
+      if (DEC && kk != warp) continue;
       uint32_t pa[4];
       pa[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
       pa[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
@@ -218,6 +227,55 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
   cp_async_wait<0>();
 
+  if constexpr (DEC) {
+    // the four warps' shares of the 16 rows meet in shared memory (the tiles are done with: the loop's last barrier)
+    constexpr int MP = DV + 2;  // a row's output, maximum and denominator
+    float* mb = reinterpret_cast<float*>(kv_s);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+      l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+      float* dst = mb + (size_t)(warp * 16 + gid + 8 * r) * MP;
+      if (tid4 == 0) {
+        dst[DV] = m[r];
+        dst[DV + 1] = l[r];
+      }
+#pragma unroll
+      for (int nt = 0; nt < 2 * VT; ++nt) {
+        dst[nt * 8 + 2 * tid4] = o[nt][2 * r];
+        dst[nt * 8 + 2 * tid4 + 1] = o[nt][2 * r + 1];
+      }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 16 * DV; e += WARPS * 32) {
+      const int rr = e / DV, d = e - rr * DV;
+      const int R = row0 + rr;
+      if (R >= total_rows) continue;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) mx = fmaxf(mx, mb[(size_t)(w * 16 + rr) * MP + DV]);
+      float acc = 0.f, den = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float* src = mb + (size_t)(w * 16 + rr) * MP;
+        if (src[DV] == -INFINITY) continue;
+        const float wgt = exp2f(src[DV] - mx);
+        den = fmaf(wgt, src[DV + 1], den);
+        acc = fmaf(wgt, src[d], acc);
+      }
+      if (splits > 1) {
+        const size_t row = ((size_t)sp * T_total + qs + R / g) * Hq + hk * g + R % g;
+        part_o[row * DV + d] = acc;
+        if (d == 0) {
+          part_ml[2 * row] = mx;
+          part_ml[2 * row + 1] = den;
+        }
+      } else {
+        out[(size_t)(qs + R / g) * ldo + (size_t)(hk * g + R % g) * DV + d] =
+            __float2bfloat16_rn(den > 0.f ? acc * (out_scale / den) : 0.f);
+      }
+    }
+  } else {
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
@@ -240,6 +298,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
     for (int nt = 0; nt < 2 * VT; ++nt)
       *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) = __floats2bfloat162_rn(o[nt][2 * r] * inv, o[nt][2 * r + 1] * inv);
+  }
   }
 }
 
@@ -266,17 +325,17 @@ __global__ void pw_attn_merge_kernel(const float* __restrict__ part_o, const flo
   }
 }
 
-template <int KT, int VT>
+template <int KT, int VT, bool DEC>
 static int pw_attn_mma_launch(const void* q, const void* k_pages, const void* v_pages, const void* pk_pages,
                               const void* pv_pages, void* out, int ldo, const int* q_start, const int* kv_len,
                               const int* table, int stride, int num_pages, const int* ptable, int pstride, int num_ppages,
                               int page_size, int B, int max_q_len, int Hq, int Hkv, float scale, float cap, float out_scale,
                               int window, int P, int T_total, float* part_o, float* part_ml, long long part_rows,
                               int* status, cudaStream_t stream) {
-  using S = PwShape<KT, VT>;
+  using S = PwShape<KT, VT, DEC>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(pw_attn_mma_kernel<KT, VT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(pw_attn_mma_kernel<KT, VT, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)S::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -289,12 +348,12 @@ static int pw_attn_mma_launch(const void* q, const void* k_pages, const void* v_
   int splits = 1;
   if (tiles == 1 && part_o && part_ml && T_total > 0) {
     const long long blocks = (long long)Hkv * B, room = part_rows / ((long long)T_total * Hq);
-    long long want = (2LL * sm_count() + blocks - 1) / blocks;
+    long long want = ((DEC ? 4LL : 2LL) * sm_count() + blocks - 1) / blocks;
     want = want < room ? want : room;
     splits = (int)(want < 1 ? 1 : (want > 32 ? 32 : want));
     if ((long long)B * splits > 65535) splits = 1;
   }
-  q3::launch(pw_attn_mma_kernel<KT, VT>, dim3((unsigned)tiles, Hkv, B * splits), dim3(S::WARPS * 32), S::SMEM_BYTES, stream,
+  q3::launch(pw_attn_mma_kernel<KT, VT, DEC>, dim3((unsigned)tiles, Hkv, B * splits), dim3(S::WARPS * 32), S::SMEM_BYTES, stream,
              (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
              (const __nv_bfloat16*)pk_pages, (const __nv_bfloat16*)pv_pages, (__nv_bfloat16*)out, ldo, q_start, kv_len, table,
              stride, num_pages, ptable, pstride, num_ppages, page_size, Hq, Hkv, scale, cap, out_scale, window, P, splits,
@@ -331,11 +390,17 @@ extern "C" int q3_pw_attn_mma(const void* q, const void* k_pages, const void* v_
       (uintptr_t)pv_pages % 16 || (uintptr_t)out % 4)
     return Q3_ERR_ALIGN;
 #define Q3_PW_CASE(KT, VT)                                                                                              \
-  if (D == 16 * KT && Dv == 16 * VT)                                                                                    \
-    return q3::pw_attn_mma_launch<KT, VT>(q, k_pages, v_pages, pk_pages, pv_pages, out, ldo, q_start, kv_len, table,    \
-                                          stride, num_pages, ptable, pstride, num_ppages, page_size, B, max_q_len, Hq,  \
-                                          Hkv, scale, cap, out_scale, window, P, T, part_o, part_ml, part_rows, status,   \
-                                          stream);
+  if (D == 16 * KT && Dv == 16 * VT) {                                                                                  \
+    if ((long long)max_q_len * (Hq / Hkv) <= 16)                                                                        \
+      return q3::pw_attn_mma_launch<KT, VT, true>(q, k_pages, v_pages, pk_pages, pv_pages, out, ldo, q_start, kv_len,   \
+                                                  table, stride, num_pages, ptable, pstride, num_ppages, page_size, B,  \
+                                                  max_q_len, Hq, Hkv, scale, cap, out_scale, window, P, T, part_o,      \
+                                                  part_ml, part_rows, status, stream);                                  \
+    return q3::pw_attn_mma_launch<KT, VT, false>(q, k_pages, v_pages, pk_pages, pv_pages, out, ldo, q_start, kv_len,    \
+                                                 table, stride, num_pages, ptable, pstride, num_ppages, page_size, B,   \
+                                                 max_q_len, Hq, Hkv, scale, cap, out_scale, window, P, T, part_o,       \
+                                                 part_ml, part_rows, status, stream);                                   \
+  }
   Q3_PW_CASE(2, 2) Q3_PW_CASE(2, 4) Q3_PW_CASE(2, 8) Q3_PW_CASE(4, 2) Q3_PW_CASE(4, 4) Q3_PW_CASE(4, 8) Q3_PW_CASE(8, 2)
   Q3_PW_CASE(8, 4) Q3_PW_CASE(8, 8)
 #undef Q3_PW_CASE
