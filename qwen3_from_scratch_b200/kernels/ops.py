@@ -2007,7 +2007,7 @@ def moe_pairs(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.
     _done("moe_pairs", code, f"experts {E}, top {top}, inner {F}")
 
 
-MOE_GROUPED_FROM = 17  # tokens from which the sorted, grouped products run (below: a pair at a time)
+MOE_GROUPED_FROM = 4  # tokens from which the sorted, grouped products run (below: a pair at a time)
 
 
 def moe_tile_rows() -> int:
