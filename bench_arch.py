@@ -208,9 +208,10 @@ class KernelClock:
         if name == "add_layernorm":
             stream, delta, out = a[0], a[1], a[4]
             return "bytes", size(stream) * (2 if delta is not None else 1) + (size(delta) if delta is not None else 0) + size(out)
-        if name == "norm_conv":
-            stream, delta, out = a[0], a[1], a[-2]
-            return "bytes", size(stream) * (2 if delta is not None else 1) + (size(delta) if delta is not None else 0) + size(out)
+        if name == "add_layernorm_conv1":
+            stream, delta, state, out = a[0], a[1], a[5], a[8]
+            n = size(stream) * (2 if delta is not None else 1) + (size(delta) if delta is not None else 0) + size(out)
+            return "bytes", n + (2 * stream.shape[0] * state.shape[1] * state.shape[2] * 4 if state is not None else 0)
         if name == "input_conv":
             return "bytes", size(a[0]) + size(a[7])
         if name == "stream_concat":
@@ -269,7 +270,7 @@ class KernelClock:
                      "sigmoid_attention", "paged_attention", "block_diag", "gemm_skinny", "gemm_skinny_normed",
                      "gemm_skinny_into_stream", "gemm_tc", "embed_scaled", "hc_norm", "act", "latent_kv_post",
                      "latent_q_post", "gate_heads", "latent_attention", "ssd_scan", "gated_group_norm", "add_layernorm",
-                     "input_conv", "stream_concat", "pw_qkv_post", "pool_blocks", "pooled_window_attention",
+                     "add_layernorm_conv1", "input_conv", "stream_concat", "pw_qkv_post", "pool_blocks", "pooled_window_attention",
                      "mingru_scan", "moe_route", "routed_experts"):
             self.wrap(ops, name, name)
         real_mm = torch.mm

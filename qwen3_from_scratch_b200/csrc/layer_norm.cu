@@ -9,6 +9,11 @@
 //                        lies before a portion comes from the request's slot of `state` (float32 [slots, K - 1, C],
 //                        zero for a new request), which a second launch renews after every reader is done.
 //
+//   add_layernorm_conv1  both of the above in one launch for a step in which every request brings one token: the
+//                        block that norms a token's row applies the convolution from the request's state and
+//                        renews the state (each thread reads and writes its own channels of it); same sums, same
+//                        order, same bits as the two kernels.
+//
 //   stream_concat        out[t] = [stream[t] + delta[t] | other[t]] in the compute dtype: the operand of a projection
 //                        that reads the stream beside a second float32 tensor of the same shape.
 //
@@ -137,6 +142,89 @@ static int add_layernorm_launch(float* stream, const void* delta, const float* w
 }
 
 }  // namespace q3
+
+namespace q3 {
+
+template <typename TD, typename TO>
+__global__ void add_layernorm_conv1_kernel(float* __restrict__ stream, const TD* __restrict__ delta,
+                                           const float* __restrict__ w, const float* __restrict__ b,
+                                           const float* __restrict__ cw, float* __restrict__ state,
+                                           const int* __restrict__ tok_seq, const int* __restrict__ slot_ids,
+                                           TO* __restrict__ out, int W, int K, int slots, float eps, int* status) {
+  extern __shared__ float row_x[];
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t r = blockIdx.x;
+  float* x = stream + r * W;
+  const TD* d = delta ? delta + r * W : nullptr;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = x[i];
+    if (d) {
+      v += to_float(d[i]);
+      x[i] = v;
+    }
+    row_x[i] = v;
+    s += v;
+  }
+  const float mean = block_sum(s, red) / (float)W;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float c = row_x[i] - mean;
+    q = fmaf(c, c, q);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(q, red) / (float)W + eps);
+  const int slot = slot_ids[tok_seq[r]];
+  const bool live = K == 1 || (slot >= 0 && slot < slots);
+  if (!live && threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+  TO* o = out + r * W;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    if (!live) {
+      o[i] = from_float<TO>(0.f);
+      continue;
+    }
+    const float h = (row_x[i] - mean) * inv * w[i] + b[i];
+    float* tail = state + (size_t)slot * (K - 1) * W + i;
+    float acc = h;
+    for (int j = 0; j < K - 1; ++j) {
+      const float v = tail[(size_t)j * W];
+      acc = fmaf(cw[(size_t)i * K + j], v, acc);
+      if (j > 0) tail[(size_t)(j - 1) * W] = v;
+    }
+    acc = fmaf(cw[(size_t)i * K + K - 1], h, acc);
+    if (K > 1) tail[(size_t)(K - 2) * W] = h;
+    o[i] = from_float<TO>(acc);
+  }
+}
+
+}  // namespace q3
+
+// stream: float32 [T, W] (+= delta in place); out [T, W] in `dtype` = h + conv(h) for h = layer norm of the row, every
+// request of the step bringing exactly one token; cw: float32 [W, K]; state: float32 [slots, K - 1, W], renewed.
+extern "C" int q3_add_layernorm_conv1(float* stream, const void* delta, const float* w, const float* b, const float* cw,
+                                      float* state, const int* tok_seq, const int* slot_ids, void* out, int dtype, int T,
+                                      int W, int K, int slots, float eps, int* status, cudaStream_t stream_) {
+  if (T <= 0) return 0;
+  if (W <= 0 || K <= 0 || K > q3::CONV_MAX_TAPS || (size_t)W * sizeof(float) > 200 * 1024) return Q3_ERR_SIZE;
+  const int threads = W >= 2048 ? 512 : (W >= 512 ? 256 : 128);
+  const size_t smem = (size_t)W * sizeof(float);
+  if (dtype == Q3_F32) {
+    auto kern = q3::add_layernorm_conv1_kernel<float, float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    q3::launch(kern, dim3(T), dim3(threads), smem, stream_, stream, (const float*)delta, w, b, cw, state, tok_seq, slot_ids,
+               (float*)out, W, K, slots, eps, status);
+  } else if (dtype == Q3_BF16) {
+    auto kern = q3::add_layernorm_conv1_kernel<__nv_bfloat16, __nv_bfloat16>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    q3::launch(kern, dim3(T), dim3(threads), smem, stream_, stream, (const __nv_bfloat16*)delta, w, b, cw, state, tok_seq,
+               slot_ids, (__nv_bfloat16*)out, W, K, slots, eps, status);
+  } else {
+    return Q3_ERR_DTYPE;
+  }
+  q3::note_stream_written();
+  return q3::launch_status();
+}
 
 // stream: float32 [T, W], += delta (compute dtype `dtype`, may be null) in place unless `rows` is given; out [n, W] in
 // float32 (`out_f32`) or in `dtype`; n = number of rows normed (T, or the length of `rows`).

@@ -43,7 +43,7 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
     const float* w = wr + (size_t)e * W;
     float dot = 0.f;
     if (by4) {
-#pragma unroll 4
+#pragma unroll 8
       for (int i = 4 * lane; i < W; i += 128) {
         const float4 wv = *reinterpret_cast<const float4*>(w + i);
         float x[4];
@@ -141,7 +141,7 @@ extern "C" int q3_moe_route(const void* h, const float* wr, const float* bias, i
                             int E, int top, float scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (W <= 0 || E <= 0 || top <= 0 || top > E || top > q3::MOE_MAX_TOP || E > 4096) return Q3_ERR_SIZE;
-  Q3_BY_DTYPE(dtype, q3::launch(q3::moe_route_kernel<E_>, dim3(T), dim3(E >= 8 ? 256 : 128), (size_t)2 * E * sizeof(float),
+  Q3_BY_DTYPE(dtype, q3::launch(q3::moe_route_kernel<E_>, dim3(T), dim3(E >= 16 ? 512 : (E >= 8 ? 256 : 128)), (size_t)2 * E * sizeof(float),
                                 stream,
                                 (const E_*)h, wr, bias, ids, wts, W, E, top, scale))
   return q3::launch_status();

@@ -143,6 +143,8 @@ _SIGNATURES = {
                             _c_float, _c_void_p],
     "q3_add_layernorm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int,
                          _c_float, _c_void_p],
+    "q3_add_layernorm_conv1": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                               _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "q3_stream_concat": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
     "q3_input_conv": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
                       _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
@@ -1718,6 +1720,36 @@ def stream_concat(stream: torch.Tensor, delta: Optional[torch.Tensor], other: to
     code = library().q3_stream_concat(stream.data_ptr(), _ptr(delta), other.data_ptr(), out.data_ptr(), dtype_tag(out.dtype),
                                       T, W, _stream())
     _done("stream_concat", code, f"width {W}")
+
+
+def add_layernorm_conv1(stream: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, bias: torch.Tensor,
+                        conv_weight: torch.Tensor, state: Optional[torch.Tensor], tok_seq: torch.Tensor,
+                        slot_ids: torch.Tensor, out: torch.Tensor, eps: float, status: torch.Tensor) -> None:
+    """``add_layernorm`` and ``input_conv`` in one launch for a step in which every request brings one token:
+    stream += delta, h = layer norm of the row, out = h + conv(h) from the request's state, which is renewed."""
+    _check("add_layernorm_conv1.stream", stream, torch.float32)
+    _check("add_layernorm_conv1.out", out)
+    for name, t in (("weight", weight), ("bias", bias), ("conv_weight", conv_weight)):
+        _check(f"add_layernorm_conv1.{name}", t, torch.float32)
+    for name, t in (("tok_seq", tok_seq), ("slot_ids", slot_ids)):
+        _check(f"add_layernorm_conv1.{name}", t, torch.int32)
+    T, W = stream.shape
+    K = conv_weight.shape[1]
+    if delta is not None:
+        _check("add_layernorm_conv1.delta", delta, out.dtype)
+    if state is not None:
+        _check("add_layernorm_conv1.state", state, torch.float32)
+    if (tuple(out.shape) != (T, W) or weight.numel() != W or bias.numel() != W or conv_weight.shape[0] != W
+            or (delta is not None and delta.shape != stream.shape) or (K > 1 and (state is None or state.dim() != 3
+            or state.shape[1] != K - 1 or state.shape[2] != W))):
+        raise KernelError(f"add_layernorm_conv1: stream {tuple(stream.shape)}, out {tuple(out.shape)}, taps "
+                          f"{tuple(conv_weight.shape)}, state {None if state is None else tuple(state.shape)}")
+    code = library().q3_add_layernorm_conv1(stream.data_ptr(), _ptr(delta), weight.data_ptr(), bias.data_ptr(),
+                                            conv_weight.data_ptr(), _ptr(state), tok_seq.data_ptr(), slot_ids.data_ptr(),
+                                            out.data_ptr(), dtype_tag(out.dtype), T, W, K,
+                                            state.shape[0] if state is not None else 0, float(eps), status.data_ptr(),
+                                            _stream())
+    _done("add_layernorm_conv1", code, f"width {W}, taps {K}")
 
 
 def input_conv(h: torch.Tensor, weight: torch.Tensor, state: Optional[torch.Tensor], q_start: torch.Tensor,

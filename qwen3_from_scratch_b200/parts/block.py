@@ -123,9 +123,12 @@ class PreNormBlock(Block):
         """What sub-layer ``which`` reads: the normed stream, through the convolution if the block has one."""
         if self.conv_taps is None:
             return norm.add_norm(stream, pending)
-        h = norm.add_norm_float32(stream, pending)
         out = self._conv_out[: stream.shape[0]]
         state = ctx.state(cache_id, ("conv1", "conv2")[which]) if self.conv_taps > 1 else None
+        if ctx.max_q_len == 1 and hasattr(norm, "add_norm_conv1"):  # single tokens: norm, convolution, state at once
+            norm.add_norm_conv1(stream, pending, self.conv_weights[which], state, ctx, out)
+            return out
+        h = norm.add_norm_float32(stream, pending)
         ops.input_conv(h, self.conv_weights[which], state, ctx.q_start, ctx.tok_seq, ctx.slot_ids, ctx.num_seqs, out,
                        self.rt.status)
         return out

@@ -137,6 +137,13 @@ class LayerNorm(Norm):
         ops.add_layernorm(stream, delta, self.weight, self.bias, out, self.eps)
         return out
 
+    def add_norm_conv1(self, stream: torch.Tensor, delta: Optional[torch.Tensor], conv_weight: torch.Tensor,
+                       state: Optional[torch.Tensor], ctx, out: torch.Tensor) -> None:
+        """For a step of single tokens: the sum, the norm, the short convolution over the normed rows from the
+        requests' states and the states' renewal in one launch."""
+        ops.add_layernorm_conv1(stream, delta, self.weight, self.bias, conv_weight, state, ctx.tok_seq, ctx.slot_ids, out,
+                                self.eps, self.rt.status)
+
     def norm_rows(self, stream: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         out = torch.empty(rows.numel(), self.dim, dtype=self.rt.dtype, device=stream.device)
         ops.add_layernorm(stream, delta, self.weight, self.bias, out, self.eps, rows=rows)

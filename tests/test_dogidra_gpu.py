@@ -97,6 +97,43 @@ def test_input_convolution_through_portions_and_slots(K):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
+@pytest.mark.parametrize("W,K", [(48, 4), (200, 2), (2048, 3), (64, 1), (4100, 5)])
+def test_norm_and_convolution_of_single_tokens_in_one_launch(W, K, dtype):
+    """A step of single tokens: the fused kernel gives the bits of the norm and the convolution one after the other,
+    for the output, the stream and the state, through slots in any order and a second step on the renewed state."""
+    from qwen3_from_scratch_b200.kernels import ops
+    g = torch.Generator().manual_seed(W + K)
+    B, slots = 5, 7
+    weight, bias = (1 + 0.3 * torch.randn(W, generator=g)).cuda(), (0.2 * torch.randn(W, generator=g)).cuda()
+    taps = (0.5 * torch.randn(W, K, generator=g)).cuda()
+    slot_ids = torch.tensor([4, 0, 6, 2, 3], dtype=torch.int32).cuda()
+    tok_seq = torch.arange(B, dtype=torch.int32).cuda()
+    q_start = torch.arange(B + 1, dtype=torch.int32).cuda()
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    state = {k: (torch.randn(slots, K - 1, W, generator=g).cuda() if K > 1 else None) for k in ("two", "one")}
+    if K > 1:
+        state["one"].copy_(state["two"])
+    stream = {k: torch.randn(B, W, generator=torch.Generator().manual_seed(3)).cuda() for k in ("two", "one")}
+    for step in range(2):
+        delta = torch.randn(B, W, generator=g).to(DT[dtype]).cuda() if step else None
+        h = torch.empty(B, W, dtype=torch.float32).cuda()
+        two, one = torch.empty(B, W, dtype=DT[dtype]).cuda(), torch.empty(B, W, dtype=DT[dtype]).cuda()
+        ops.add_layernorm(stream["two"], delta, weight, bias, h, 1e-5)
+        ops.input_conv(h, taps, state["two"], q_start, tok_seq, slot_ids, B, two, status)
+        ops.add_layernorm_conv1(stream["one"], delta, weight, bias, taps, state["one"], tok_seq, slot_ids, one, 1e-5, status)
+        assert torch.equal(one, two) and torch.equal(stream["one"], stream["two"])
+        assert K == 1 or torch.equal(state["one"], state["two"])
+        x = stream["two"].double()
+        hh = (x - x.mean(-1, keepdim=True)) / torch.sqrt(x.var(-1, unbiased=False, keepdim=True) + 1e-5) * weight.double() \
+            + bias.double()
+        if step == 0 and K > 1:
+            first = state["two"][slot_ids.long()].double().clone()  # after the step: the older entries moved up
+            assert torch.equal(first[:, -1].float(), h)
+        close(h, hh, "float32", "the normed rows")
+    assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("dtype", list(DT))
 @pytest.mark.parametrize("W,E,top", [(40, 6, 2), (64, 5, 1), (100, 4, 4), (72, 33, 8), (2048, 64, 6)])
 def test_router_choice_and_weights(W, E, top, dtype):
     from qwen3_from_scratch_b200.kernels import ops
