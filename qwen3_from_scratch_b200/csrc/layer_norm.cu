@@ -237,6 +237,45 @@ extern "C" int q3_add_layernorm(float* stream, const void* delta, const float* w
 }
 
 // h: float32 [T, C]; w: float32 [C, K]; state: float32 [slots, K - 1, C] (unused for K = 1); out [T, C] in `dtype`.
+namespace q3 {
+
+// The same sums for four channels per thread (C a multiple of 4, 16-byte aligned rows): one 16-byte load per tap.
+template <typename TO>
+__global__ void input_conv_vec4_kernel(const float* __restrict__ h, const float* __restrict__ w,
+                                       const float* __restrict__ state, const int* __restrict__ q_start,
+                                       const int* __restrict__ tok_seq, const int* __restrict__ slot_ids,
+                                       TO* __restrict__ out, int T, int C, int K, int slots, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+  const int t = blockIdx.y;
+  if (c >= C) return;
+  const int b = tok_seq[t];
+  const int s0 = q_start[b], slot = slot_ids[b];
+  TO* o = out + (size_t)t * C + c;
+  if (K > 1 && (slot < 0 || slot >= slots)) {
+    if (threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = from_float<TO>(0.f);
+    return;
+  }
+  const float4 own = *reinterpret_cast<const float4*>(h + (size_t)t * C + c);
+  float acc[4] = {own.x, own.y, own.z, own.w};
+  for (int j = 0; j < K; ++j) {
+    const int src = t - (K - 1) + j;
+    const float4 v = *reinterpret_cast<const float4*>(
+        src >= s0 ? h + (size_t)src * C + c : state + ((size_t)slot * (K - 1) + (K - 1 + src - s0)) * C + c);
+    acc[0] = fmaf(w[(size_t)(c + 0) * K + j], v.x, acc[0]);
+    acc[1] = fmaf(w[(size_t)(c + 1) * K + j], v.y, acc[1]);
+    acc[2] = fmaf(w[(size_t)(c + 2) * K + j], v.z, acc[2]);
+    acc[3] = fmaf(w[(size_t)(c + 3) * K + j], v.w, acc[3]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = from_float<TO>(acc[i]);
+}
+
+}  // namespace q3
+
 extern "C" int q3_input_conv(const float* h, const float* w, float* state, const int* q_start, const int* tok_seq,
                              const int* slot_ids, void* out, int dtype, int T, int B, int C, int K, int slots,
                              int renew_state, int* status, cudaStream_t stream) {
@@ -244,7 +283,15 @@ extern "C" int q3_input_conv(const float* h, const float* w, float* state, const
   if (C <= 0 || K <= 0 || K > q3::CONV_MAX_TAPS || B <= 0 || T > 65535 || B > 65535) return Q3_ERR_SIZE;
   const int threads = 128;
   const dim3 grid((C + threads - 1) / threads, T);
-  if (dtype == Q3_F32)
+  const bool vec4 = C % 4 == 0 && (uintptr_t)h % 16 == 0 && (K == 1 || (uintptr_t)state % 16 == 0);
+  const dim3 grid4((C / 4 + threads - 1) / threads, T);
+  if (vec4 && dtype == Q3_F32)
+    q3::launch(q3::input_conv_vec4_kernel<float>, grid4, dim3(threads), 0, stream, h, w, (const float*)state, q_start,
+               tok_seq, slot_ids, (float*)out, T, C, K, slots, status);
+  else if (vec4 && dtype == Q3_BF16)
+    q3::launch(q3::input_conv_vec4_kernel<__nv_bfloat16>, grid4, dim3(threads), 0, stream, h, w, (const float*)state,
+               q_start, tok_seq, slot_ids, (__nv_bfloat16*)out, T, C, K, slots, status);
+  else if (dtype == Q3_F32)
     q3::launch(q3::input_conv_kernel<float>, grid, dim3(threads), 0, stream, h, w, (const float*)state, q_start, tok_seq,
                slot_ids, (float*)out, T, C, K, slots, status);
   else if (dtype == Q3_BF16)

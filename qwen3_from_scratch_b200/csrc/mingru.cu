@@ -19,7 +19,7 @@
 
 namespace q3 {
 
-constexpr int MG_CHUNK = 64;
+constexpr int MG_CHUNK = 32;
 
 template <typename T>
 __global__ void mingru_scan_kernel(const T* __restrict__ proj, int ld, int z_col, int u_col, int g_col,
@@ -70,7 +70,7 @@ __global__ void mingru_chunk_kernel(const T* __restrict__ proj, int ld, int z_co
   float* sc = scratch + ((size_t)(q_start[b] / MG_CHUNK + b + j) * 2) * C + c;
   const float zb = bz[c], ub = bu[c];
   float S = PASS == 3 ? sc[0] : 0.f, P = 1.f;
-#pragma unroll 4
+#pragma unroll 8
   for (int t = t0; t < t1; ++t) {
     const T* row = proj + (size_t)t * ld;
     const float z = mg_sigmoid(to_float(row[z_col + c]) + zb);
