@@ -274,6 +274,81 @@ __global__ void input_conv_vec4_kernel(const float* __restrict__ h, const float*
   for (int i = 0; i < 4; ++i) o[i] = from_float<TO>(acc[i]);
 }
 
+// The same sums again for a run of CONV_RUN tokens and four channels per thread, K known at compile time: the run's
+// rows and the K - 1 before it are asked for at once and stay in registers, so that a row is loaded once per run
+// instead of once per tap; a token whose portion starts inside the window takes the older rows from the state.
+constexpr int CONV_RUN = 8;
+
+template <typename TO, int K>
+__global__ void input_conv_run_kernel(const float* __restrict__ h, const float* __restrict__ w,
+                                      const float* __restrict__ state, const int* __restrict__ q_start,
+                                      const int* __restrict__ tok_seq, const int* __restrict__ slot_ids,
+                                      TO* __restrict__ out, int T, int C, int slots, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int c = 4 * (blockIdx.x * blockDim.x + threadIdx.x);
+  const int t0 = blockIdx.y * CONV_RUN;
+  if (c >= C) return;
+  float4 win[CONV_RUN + K - 1];
+#pragma unroll
+  for (int i = 0; i < CONV_RUN + K - 1; ++i) {
+    const int src = t0 - (K - 1) + i;
+    win[i] = (src >= 0 && src < T) ? *reinterpret_cast<const float4*>(h + (size_t)src * C + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float wk[4][K];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < K; ++j) wk[i][j] = w[(size_t)(c + i) * K + j];
+#pragma unroll
+  for (int r = 0; r < CONV_RUN; ++r) {
+    const int t = t0 + r;
+    if (t >= T) break;
+    const int b = tok_seq[t];
+    const int s0 = q_start[b], slot = slot_ids[b];
+    TO* o = out + (size_t)t * C + c;
+    const bool live = K == 1 || (slot >= 0 && slot < slots);
+    if (!live) {
+      if (threadIdx.x == 0) atomicOr(status, Q3_STATUS_BAD_POSITION);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[i] = from_float<TO>(0.f);
+      continue;
+    }
+    const float4 own = win[r + K - 1];
+    float acc[4] = {own.x, own.y, own.z, own.w};
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int src = t - (K - 1) + j;
+      float4 v = win[r + j];
+      if (src < s0) v = *reinterpret_cast<const float4*>(state + ((size_t)slot * (K - 1) + (K - 1 + src - s0)) * C + c);
+      acc[0] = fmaf(wk[0][j], v.x, acc[0]);
+      acc[1] = fmaf(wk[1][j], v.y, acc[1]);
+      acc[2] = fmaf(wk[2][j], v.z, acc[2]);
+      acc[3] = fmaf(wk[3][j], v.w, acc[3]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o[i] = from_float<TO>(acc[i]);
+  }
+}
+
+template <typename TO>
+static bool input_conv_run_launch(const float* h, const float* w, const float* state, const int* q_start, const int* tok_seq,
+                                  const int* slot_ids, void* out, int T, int C, int K, int slots, int* status,
+                                  cudaStream_t stream) {
+  const int threads = 64;
+  const dim3 grid((C / 4 + threads - 1) / threads, (T + CONV_RUN - 1) / CONV_RUN);
+#define Q3_CONV_RUN_CASE(KK)                                                                                       \
+  if (K == KK) {                                                                                                   \
+    launch(input_conv_run_kernel<TO, KK>, grid, dim3(threads), 0, stream, h, w, state, q_start, tok_seq, slot_ids, \
+           (TO*)out, T, C, slots, status);                                                                         \
+    return true;                                                                                                   \
+  }
+  Q3_CONV_RUN_CASE(2) Q3_CONV_RUN_CASE(3) Q3_CONV_RUN_CASE(4) Q3_CONV_RUN_CASE(5) Q3_CONV_RUN_CASE(6) Q3_CONV_RUN_CASE(7)
+  Q3_CONV_RUN_CASE(8)
+#undef Q3_CONV_RUN_CASE
+  return false;
+}
+
 }  // namespace q3
 
 extern "C" int q3_input_conv(const float* h, const float* w, float* state, const int* q_start, const int* tok_seq,
@@ -285,7 +360,15 @@ extern "C" int q3_input_conv(const float* h, const float* w, float* state, const
   const dim3 grid((C + threads - 1) / threads, T);
   const bool vec4 = C % 4 == 0 && (uintptr_t)h % 16 == 0 && (K == 1 || (uintptr_t)state % 16 == 0);
   const dim3 grid4((C / 4 + threads - 1) / threads, T);
-  if (vec4 && dtype == Q3_F32)
+  // many tokens: runs of tokens per thread (taps 2 .. 8)
+  const bool runs = vec4 && T >= 4 * q3::CONV_RUN && (dtype == Q3_F32 || dtype == Q3_BF16);
+  if (runs && dtype == Q3_F32 &&
+      q3::input_conv_run_launch<float>(h, w, (const float*)state, q_start, tok_seq, slot_ids, out, T, C, K, slots, status,
+                                       stream)) {
+  } else if (runs && dtype == Q3_BF16 &&
+             q3::input_conv_run_launch<__nv_bfloat16>(h, w, (const float*)state, q_start, tok_seq, slot_ids, out, T, C, K,
+                                                      slots, status, stream)) {
+  } else if (vec4 && dtype == Q3_F32)
     q3::launch(q3::input_conv_vec4_kernel<float>, grid4, dim3(threads), 0, stream, h, w, (const float*)state, q_start,
                tok_seq, slot_ids, (float*)out, T, C, K, slots, status);
   else if (vec4 && dtype == Q3_BF16)

@@ -96,6 +96,37 @@ def test_input_convolution_through_portions_and_slots(K):
         close(torch.cat(got[r]), want[r][:fed[r]], "float32", f"taps {K} request {r}", tol=1e-6)
 
 
+@pytest.mark.parametrize("K", [1, 2, 4, 8, 9])
+def test_input_convolution_of_long_portions_beside_each_other(K):
+    """Portions long enough for the kernel that walks runs of tokens (and, for taps it has no form for, the one that
+    takes four channels at a time): requests that start and end inside a run, a portion after a single token."""
+    from qwen3_from_scratch_b200.kernels import ops
+    C, slots = 136, 4
+    g = torch.Generator().manual_seed(K + 20)
+    w = torch.randn(C, K, generator=g)
+    h_of = {"a": torch.randn(150, C, generator=g), "b": torch.randn(77, C, generator=g)}
+    want = {r: plain.input_conv(h.double(), w.double(), torch.zeros(K - 1, C, dtype=F64))[0] for r, h in h_of.items()}
+    state = torch.zeros(slots, max(K - 1, 1), C).cuda()
+    slot_of, fed, got = {"a": 3, "b": 1}, {"a": 0, "b": 0}, {"a": [], "b": []}
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for step in ([("a", 1)], [("a", 50), ("b", 37)], [("b", 40), ("a", 99)]):
+        rows = torch.cat([h_of[r][fed[r]:fed[r] + n] for r, n in step]).cuda()
+        starts = [0]
+        for _, n in step:
+            starts.append(starts[-1] + n)
+        q_start = torch.tensor(starts, dtype=torch.int32, device="cuda")
+        tok_seq = torch.tensor([i for i, (_, n) in enumerate(step) for _ in range(n)], dtype=torch.int32, device="cuda")
+        slot_ids = torch.tensor([slot_of[r] for r, _ in step], dtype=torch.int32, device="cuda")
+        out = torch.empty(rows.shape[0], C, device="cuda")
+        ops.input_conv(rows, w.cuda(), state if K > 1 else None, q_start, tok_seq, slot_ids, len(step), out, status)
+        for i, (r, n) in enumerate(step):
+            got[r].append(out[starts[i]:starts[i + 1]].cpu())
+            fed[r] += n
+    assert int(status.item()) == 0
+    for r in h_of:
+        close(torch.cat(got[r]), want[r], "float32", f"taps {K} request {r}", tol=1e-6)
+
+
 @pytest.mark.parametrize("dtype", list(DT))
 @pytest.mark.parametrize("W,K", [(48, 4), (200, 2), (2048, 3), (64, 1), (4100, 5)])
 def test_norm_and_convolution_of_single_tokens_in_one_launch(W, K, dtype):
