@@ -56,9 +56,9 @@ DOGIDRA_Y = {
 DOGIDRA_Z = {
     "architecture": "Dogidra", "vocab": 300, "width": 128, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-6},
     "canon": {"taps": 2}, "loop": {"start": 0, "stop": 2, "times": 2},
-    "layers": [layer(8, 2, 64, 64, 0.125, 64, 16, 1000000.0, 64, 128, 0.6, 0.9, softcap=30.0,
-                     scaling=(8.0, 256, 16.0, 2.0), moe=(8, 2, 64, 2.0, 128)),
-               layer(4, 1, 128, 128, 0.09, 48, 32, 10000.0, 64, 256, 1.0, 1.0, moe=(16, 4, 64, 1.0, 64))]}
+    "layers": [layer(8, 2, 64, 64, 0.11, 64, 16, 1000000.0, 64, 128, 0.8, 1.1, softcap=20.0,
+                     scaling=(6.0, 256, 16.0, 2.0), moe=(8, 2, 72, 1.75, 192)),
+               layer(4, 1, 128, 128, 0.09, 48, 32, 10000.0, 64, 256, 1.0, 1.0, moe=(12, 4, 48, 1.0, 64))]}
 CONFIGS = {"x": (DOGIDRA_X, 3), "y": (DOGIDRA_Y, 4), "z": (DOGIDRA_Z, 5)}
 
 
