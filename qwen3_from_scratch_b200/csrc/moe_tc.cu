@@ -376,13 +376,13 @@ extern "C" int q3_moe_grouped(const void* h, const void* up, const void* down, c
     const long long t256 = expect * ((n + 255) / 256), t128 = expect * ((n + 127) / 128);
     return ((t256 + sms - 1) / sms) * 256 <= ((t128 + sms - 1) / sms) * 128;
   };
-  code = wide(F) ? q3::moe_grouped_launch<256>(sorted_in, up, sorted_act, meta, map_tiles, max_tiles, F, W, E, F, act, status, stream)
-                 : q3::moe_grouped_launch<128>(sorted_in, up, sorted_act, meta, map_tiles, max_tiles, F, W, E, F, act, status, stream);
+  auto product = [&](const void* a, const void* wgt, void* c, int n, int k, int activation) {
+    return wide(n) ? q3::moe_grouped_launch<256>(a, wgt, c, meta, map_tiles, max_tiles, n, k, E, n, activation, status, stream)
+                   : q3::moe_grouped_launch<128>(a, wgt, c, meta, map_tiles, max_tiles, n, k, E, n, activation, status, stream);
+  };
+  code = product(sorted_in, up, sorted_act, F, W, act);
   if (code) return code;
-  code = wide(W) ? q3::moe_grouped_launch<256>(sorted_act, down, sorted_out, meta, map_tiles, max_tiles, W, F, E, W, Q3_ACT_NONE, status,
-                                               stream)
-                 : q3::moe_grouped_launch<128>(sorted_act, down, sorted_out, meta, map_tiles, max_tiles, W, F, E, W, Q3_ACT_NONE, status,
-                                               stream);
+  code = product(sorted_act, down, sorted_out, W, F, Q3_ACT_NONE);
   if (code) return code;
   q3::launch(q3::moe_combine_kernel, dim3(T), dim3(128), 0, stream, (const bf16*)sorted_out, (const int*)pos, wts,
              (const bf16*)base, (bf16*)out, W, top);

@@ -13,6 +13,7 @@
 //   pool_blocks      the blocks that this step completed: their means into the block pages
 //   pw_attn_ref      a warp per (token, head), blocks first and then tokens, one by one in ascending order, float32
 //                    arithmetic: the float32 run's kernel, the fallback for every shape and the other kernels' oracle
+// The bfloat16 run's kernel for heads of 32, 64 or 128 values (tensor cores) is in pooled_attn_mma.cu.
 #include "common.cuh"
 
 namespace q3 {
