@@ -11,7 +11,8 @@ Pages are taken incrementally as a request grows (the reference's ``allocate``/`
 inference/block_manager.py:85-106) and given back
   * when the request ends or is preempted (``close``), and
   * in a group with a window, as soon as every position of a page is older than any
-    later query can see (``advance``); its table entry becomes -1.
+    later query can see (``advance``); its table entry becomes -1.  Pages that hold one of the
+    request's first ``keep_first`` tokens (``PagedCacheSpec.keep_first``) are never given back this way.
 A page given back is handed out again at once (LIFO), so tests see reuse quickly.
 
 Beside the pages there are ``max_seqs`` slots for state of fixed size; a request holds one
@@ -269,7 +270,8 @@ class CacheManager:
         r.length = new_length
         for g, pool in enumerate(self._pools):
             keep_from = min(self._first_needed_page(g, new_length), len(r.tables[g]))
-            for i in range(r.first_live[g], keep_from):
+            kept_first = -(-self.layout.groups[g].spec.keep_first // self.page_size)  # pages with first tokens to keep
+            for i in range(max(r.first_live[g], kept_first), keep_from):
                 page = r.tables[g][i]
                 if page >= 0:
                     pool.give_back(page, req)

@@ -1,0 +1,153 @@
+// Dynamic Tanh in place of a norm (Zhu et al., "Transformers without Normalization"): y = tanh(alpha x) w + b with a
+// scalar alpha and a weight and bias per feature; no mean, no variance, nothing reduced over the row.  And what a
+// block with such "norms" on both sides of every sub-layer does to the float32 residual stream between two products:
+//
+//   add_dyt        stream += after(delta) + rows_add + vec_add (each part optional; `after` is the Dynamic Tanh that
+//                  follows a sub-layer, applied to its output `delta`), then out = before(stream) (`before`: the one
+//                  in front of the next sub-layer, or none: out is the stream in the compute dtype); with `rows` the
+//                  same for chosen rows only, the stream left as it is (the model's last norm)
+//   side_gate      g = gelu_tanh(p) * e: p a product of the stream, e a slice of a token's row of a second embedding
+//   add_unit_rms   stream += y / sqrt(mean(y^2) + eps) * w: a product's rows brought to unit root mean square, a
+//                  weight per feature, added into the stream
+//   sigmoid_gate   x *= sigmoid(g) element by element (an attention's output gate)
+//
+// All arithmetic float32; alpha is read from device memory (a tensor of the model, no host copy).
+#include "common.cuh"
+
+namespace q3 {
+
+struct DytParams {
+  const float* alpha;  // one value; null: the identity
+  const float* w;
+  const float* b;
+};
+
+__device__ __forceinline__ float dyt(float x, float alpha, const float* w, const float* b, int c) {
+  return fmaf(tanhf(alpha * x), w[c], b[c]);
+}
+
+// grid (ceil(W / (4 * 128)) , rows).  `rows` (or null): the rows to work on, the stream then stays as it is.
+template <typename T, typename O>
+__global__ void add_dyt_kernel(float* __restrict__ stream, const T* __restrict__ delta, DytParams after,
+                               const float* __restrict__ rows_add, const float* __restrict__ vec_add, DytParams before,
+                               O* __restrict__ out, const int* __restrict__ rows, int W) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.y;
+  const int t = rows ? rows[r] : r;
+  const float a_after = after.alpha ? *after.alpha : 0.f, a_before = before.alpha ? *before.alpha : 0.f;
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < W; c += gridDim.x * blockDim.x) {
+    const size_t i = (size_t)t * W + c;
+    float x = stream[i];
+    if (delta) {
+      const float d = to_float(delta[i]);
+      x += after.alpha ? dyt(d, a_after, after.w, after.b, c) : d;
+    }
+    if (rows_add) x += rows_add[i];
+    if (vec_add) x += vec_add[c];
+    if (!rows) stream[i] = x;
+    if (out) out[(size_t)r * W + c] = from_float<O>(before.alpha ? dyt(x, a_before, before.w, before.b, c) : x);
+  }
+}
+
+// grid (T).  p: [T, dim] in the compute dtype; side: float32 [T, ld], the layer's slice at column `col`.
+template <typename T>
+__global__ void side_gate_kernel(const T* __restrict__ p, const float* __restrict__ side, int ld, int col,
+                                 T* __restrict__ out, int dim) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  for (int j = threadIdx.x; j < dim; j += blockDim.x)
+    out[(size_t)t * dim + j] = from_float<T>(gelu_tanh_f(to_float(p[(size_t)t * dim + j])) * side[(size_t)t * ld + col + j]);
+}
+
+// grid (T), one block per row; the sum of squares in the block's fixed order.
+template <typename T>
+__global__ void add_unit_rms_kernel(float* __restrict__ stream, const T* __restrict__ y, const float* __restrict__ w,
+                                    float eps, int W) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const T* row = y + (size_t)t * W;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    const float v = to_float(row[c]);
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) stream[(size_t)t * W + c] += to_float(row[c]) * inv * w[c];
+}
+
+// grid (ceil(n / 256), T).  x: rows of ldx values, n of them from column 0; g: rows of ldg values, the gates'
+// pre-activations from column g_col.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, int ldx, const T* __restrict__ g, int ldg, int g_col, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= n) return;
+  T* v = x + (size_t)t * ldx + c;
+  *v = from_float<T>(to_float(*v) * sigmoid_f(to_float(g[(size_t)t * ldg + g_col + c])));
+}
+
+}  // namespace q3
+
+#define Q3_BY_DTYPE(dtype, CALL)                 \
+  if ((dtype) == Q3_F32) { using E = float; CALL; }  \
+  else if ((dtype) == Q3_BF16) { using E = __nv_bfloat16; CALL; } \
+  else return Q3_ERR_DTYPE;
+
+// stream: float32 [T, W]; delta: [T, W] in `dtype` or null; after_* / before_*: alpha (one float32 on the device),
+// weight and bias (float32 [W]) of the Dynamic Tanh after the sub-layer / before the next, alpha null for none;
+// rows_add: float32 [T, W] or null; vec_add: float32 [W] or null; out: [R, W] in `dtype` (float32 with out_f32) or
+// null; rows: int32 [R] or null (then R = T and the stream is updated).
+extern "C" int q3_add_dyt(float* stream, const void* delta, const float* after_alpha, const float* after_w,
+                          const float* after_b, const float* rows_add, const float* vec_add, const float* before_alpha,
+                          const float* before_w, const float* before_b, void* out, int out_f32, const int* rows, int R,
+                          int dtype, int T, int W, cudaStream_t cuda_stream) {
+  const int n = rows ? R : T;
+  if (n <= 0) return 0;
+  if (W <= 0 || n > 65535 * 32) return Q3_ERR_SIZE;
+  const q3::DytParams after{after_alpha, after_w, after_b}, before{before_alpha, before_w, before_b};
+  const dim3 grid((unsigned)((W + 1023) / 1024 > 0 ? (W + 1023) / 1024 : 1), (unsigned)n), block(256);
+  if (n > 65535) return Q3_ERR_SIZE;
+  if (out_f32) {
+    Q3_BY_DTYPE(dtype, q3::launch(q3::add_dyt_kernel<E, float>, grid, block, 0, cuda_stream, stream, (const E*)delta, after,
+                                  rows_add, vec_add, before, (float*)out, rows, W))
+  } else {
+    Q3_BY_DTYPE(dtype, q3::launch(q3::add_dyt_kernel<E, E>, grid, block, 0, cuda_stream, stream, (const E*)delta, after,
+                                  rows_add, vec_add, before, (E*)out, rows, W))
+  }
+  if (!rows) q3::note_stream_written();
+  return q3::launch_status();
+}
+
+extern "C" int q3_side_gate(const void* p, const float* side, int ld, int col, void* out, int dtype, int T, int dim,
+                            cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dim <= 0 || col < 0 || col + dim > ld) return Q3_ERR_SIZE;
+  Q3_BY_DTYPE(dtype, q3::launch(q3::side_gate_kernel<E>, dim3(T), dim3(dim >= 256 ? 256 : (dim >= 64 ? 64 : 32)), 0, stream,
+                                (const E*)p, side, ld, col, (E*)out, dim))
+  return q3::launch_status();
+}
+
+extern "C" int q3_add_unit_rms(float* stream, const void* y, const float* w, float eps, int dtype, int T, int W,
+                               cudaStream_t cuda_stream) {
+  if (T <= 0) return 0;
+  if (W <= 0) return Q3_ERR_SIZE;
+  Q3_BY_DTYPE(dtype, q3::launch(q3::add_unit_rms_kernel<E>, dim3(T), dim3(W >= 1024 ? 256 : 128), 0, cuda_stream, stream,
+                                (const E*)y, w, eps, W))
+  q3::note_stream_written();
+  return q3::launch_status();
+}
+
+extern "C" int q3_sigmoid_gate(void* x, int ldx, const void* g, int ldg, int g_col, int n, int dtype, int T,
+                               cudaStream_t stream) {
+  if (T <= 0 || n <= 0) return 0;
+  if (T > 65535 || ldx < n || g_col < 0 || g_col + n > ldg) return Q3_ERR_SIZE;
+  Q3_BY_DTYPE(dtype, q3::launch(q3::sigmoid_gate_kernel<E>, dim3((n + 255) / 256, T), dim3(256), 0, stream, (E*)x, ldx,
+                                (const E*)g, ldg, g_col, n))
+  return q3::launch_status();
+}

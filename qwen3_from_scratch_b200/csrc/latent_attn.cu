@@ -9,9 +9,11 @@
 //                    arithmetic; the float32 run's kernel, every shape's fallback and the other kernels' oracle)
 //   gate_heads       head outputs [H, T, dv] float32 times their gates -> [T, H dv] in the compute dtype
 //
-// Rotation: dimension i of the first `dims` of a rotated part is paired with i + dims / 2; the angle is
-// position * freq[i] in float32 and sine and cosine are multiplied by `mag` (the frequencies and the magnitude
-// carry whatever stretching the model uses; the kernel only applies them).
+// Rotation: dimension i of the first `dims` of a rotated part is paired with i + dims / 2 (`pairing` 0, halves) or
+// dimension 2i with 2i + 1 (`pairing` 1, neighbours); the angle is position * freq[i] in float32 and sine and cosine
+// are multiplied by `mag` (the frequencies and the magnitude carry whatever stretching the model uses; the kernel
+// only applies them).  A sink (`sink`, one number per head, or null) is a term exp(sink_h) in the softmax's
+// denominator that has no key and no value and is not scaled.
 #include "common.cuh"
 
 namespace q3 {
@@ -21,17 +23,19 @@ constexpr int LA_PER = 16;      // latent values per lane: rank up to 512
 constexpr int LA_ROT_PER = 4;   // rotated values per lane: rot up to 128
 
 template <typename T>
-__device__ __forceinline__ float rotated(const T* v, int i, int dims, const float* __restrict__ freq, float pos, float mag) {
+__device__ __forceinline__ float rotated(const T* v, int i, int dims, const float* __restrict__ freq, float pos, float mag,
+                                         int pairing) {
   // value i of the vector v after rotation; values from `dims` on pass unchanged
   if (i >= dims) return to_float(v[i]);
   const int half = dims >> 1;
-  const int p = i < half ? i : i - half;
+  const int p = pairing ? i >> 1 : (i < half ? i : i - half);
+  const bool first = pairing ? !(i & 1) : i < half;
   float s, c;
   sincosf(pos * freq[p], &s, &c);
   s *= mag;
   c *= mag;
-  const float a = to_float(v[p]), b = to_float(v[p + half]);
-  return i < half ? a * c - b * s : b * c + a * s;
+  const float a = to_float(v[pairing ? 2 * p : p]), b = to_float(v[pairing ? 2 * p + 1 : p + half]);
+  return first ? a * c - b * s : b * c + a * s;
 }
 
 // One block per token.  proj: [T, ld]: the query latent's pre-norm values at column 0 (q_rank of them), then the
@@ -43,7 +47,7 @@ __global__ void latent_kv_post_kernel(const T* __restrict__ proj, int ld, int q_
                                       const int* __restrict__ positions, const int* __restrict__ tok_seq,
                                       const int* __restrict__ table, int stride, int page_size, int num_pages,
                                       T* __restrict__ cq, T* __restrict__ c_pages, T* __restrict__ r_pages,
-                                      float* __restrict__ gate, int write_cache, int* status) {
+                                      float* __restrict__ gate, int write_cache, int pairing, int* status) {
   __shared__ float red[32];
   pdl_wait();
   pdl_launch_dependents();
@@ -62,8 +66,9 @@ __global__ void latent_kv_post_kernel(const T* __restrict__ proj, int ld, int q_
   const float rk = rsqrtf(block_sum(ssk, red) / (float)rank + eps);
   for (int i = threadIdx.x; i < q_rank; i += blockDim.x)
     cq[(size_t)t * q_rank + i] = from_float<T>(to_float(row[i]) * rq * wq[i]);
-  for (int h = threadIdx.x; h < H; h += blockDim.x)
-    gate[(size_t)t * H + h] = sigmoid_f(to_float(row[gate_col + h]));
+  if (gate)
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+      gate[(size_t)t * H + h] = sigmoid_f(to_float(row[gate_col + h]));
   if (!write_cache) return;
   const int pos = positions[t], b = tok_seq[t];
   if (pos < 0 || b < 0) {
@@ -79,7 +84,7 @@ __global__ void latent_kv_post_kernel(const T* __restrict__ proj, int ld, int q_
   for (int i = threadIdx.x; i < rank; i += blockDim.x)
     c_pages[slot * rank + i] = from_float<T>(to_float(row[kv_col + i]) * rk * wkv[i]);
   for (int i = threadIdx.x; i < rot; i += blockDim.x)
-    r_pages[slot * rot + i] = from_float<T>(rotated(row + kv_col + rank, i, dims, freq, (float)pos, mag));
+    r_pages[slot * rot + i] = from_float<T>(rotated(row + kv_col + rank, i, dims, freq, (float)pos, mag, pairing));
 }
 
 // One block per token.  q: [T, H, dn + rot] -> q_plain [T, H * dn] and q_rot [T, H, rot] (rotated).  The token's
@@ -87,7 +92,7 @@ __global__ void latent_kv_post_kernel(const T* __restrict__ proj, int ld, int q_
 template <typename T>
 __global__ void latent_q_post_kernel(const T* __restrict__ q, int H, int dn, int rot, int dims,
                                      const float* __restrict__ freq, float mag, const int* __restrict__ positions,
-                                     T* __restrict__ q_plain, T* __restrict__ q_rot) {
+                                     T* __restrict__ q_plain, T* __restrict__ q_rot, int pairing) {
   extern __shared__ float cs_table[];  // [dims / 2] cosines, then [dims / 2] sines
   pdl_wait();
   pdl_launch_dependents();
@@ -115,9 +120,11 @@ __global__ void latent_q_post_kernel(const T* __restrict__ q, int H, int dn, int
     if (r >= dims) {
       out = to_float(v[r]);
     } else {
-      const int p = r < half ? r : r - half;
-      const float a = to_float(v[p]), b = to_float(v[p + half]), c = cs_table[p], sn = cs_table[half + p];
-      out = r < half ? a * c - b * sn : b * c + a * sn;
+      const int p = pairing ? r >> 1 : (r < half ? r : r - half);
+      const bool first = pairing ? !(r & 1) : r < half;
+      const float a = to_float(v[pairing ? 2 * p : p]), b = to_float(v[pairing ? 2 * p + 1 : p + half]);
+      const float c = cs_table[p], sn = cs_table[half + p];
+      out = first ? a * c - b * sn : b * c + a * sn;
     }
     q_rot[((size_t)t * H + h) * rot + r] = from_float<T>(out);
   }
@@ -130,7 +137,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32)
 latent_attn_ref_kernel(const float* __restrict__ q_abs, const T* __restrict__ q_rot, const T* __restrict__ c_pages,
                        const T* __restrict__ r_pages, const int* __restrict__ positions, const int* __restrict__ tok_seq,
                        const int* __restrict__ table, int stride, int page_size, int num_pages, T* __restrict__ out,
-                       int Ttot, int H, int rank, int rot, float scale, int* status) {
+                       int Ttot, int H, int rank, int rot, float scale, const float* __restrict__ sink, int* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -190,7 +197,13 @@ latent_attn_ref_kernel(const float* __restrict__ q_abs, const T* __restrict__ q_
       m = m_new;
     }
   }
-  const float inv = l > 0.f ? 1.0f / l : 0.f;
+  float keep = 1.f;
+  if (sink) {  // one more term in the denominator, after the last key
+    const float m_new = fmaxf(m, sink[h]);
+    keep = expf(m - m_new);
+    l = fmaf(l, keep, expf(sink[h] - m_new));
+  }
+  const float inv = l > 0.f ? keep / l : 0.f;
 #pragma unroll
   for (int k = 0; k < LA_PER; ++k) {
     const int r = lane + 32 * k;
@@ -198,7 +211,7 @@ latent_attn_ref_kernel(const float* __restrict__ q_abs, const T* __restrict__ q_
   }
 }
 
-// out[t, h * dv + v] = o[h, t, v] * gate[t, h]
+// out[t, h * dv + v] = o[h, t, v] * gate[t, h] (without gates: the heads laid side by side)
 template <typename T>
 __global__ void gate_heads_kernel(const float* __restrict__ o, const float* __restrict__ gate, T* __restrict__ out,
                                   int Ttot, int H, int dv) {
@@ -207,7 +220,7 @@ __global__ void gate_heads_kernel(const float* __restrict__ o, const float* __re
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < H * dv; i += blockDim.x) {
     const int h = i / dv, v = i - h * dv;
-    out[(size_t)t * H * dv + i] = from_float<T>(o[((size_t)h * Ttot + t) * dv + v] * gate[(size_t)t * H + h]);
+    out[(size_t)t * H * dv + i] = from_float<T>(o[((size_t)h * Ttot + t) * dv + v] * (gate ? gate[(size_t)t * H + h] : 1.f));
   }
 }
 
@@ -222,30 +235,31 @@ extern "C" int q3_latent_kv_post(const void* proj, int ld, int q_rank, int kv_co
                                  int H, const float* wq, const float* wkv, float eps, const float* freq, float mag,
                                  const int* positions, const int* tok_seq, const int* table, int stride, int page_size,
                                  int num_pages, void* cq, void* c_pages, void* r_pages, float* gate, int write_cache,
-                                 int dtype, int T, int* status, cudaStream_t stream) {
+                                 int dtype, int T, int pairing, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (q_rank <= 0 || rank <= 0 || rot < 0 || dims < 0 || dims > rot || dims % 2 || H <= 0 || page_size <= 0 || stride <= 0)
     return Q3_ERR_SIZE;
   Q3_BY_DTYPE(dtype, q3::launch(q3::latent_kv_post_kernel<E>, dim3(T), dim3(128), 0, stream, (const E*)proj, ld, q_rank,
                                 kv_col, rank, rot, dims, gate_col, H, wq, wkv, eps, freq, mag, positions, tok_seq, table,
-                                stride, page_size, num_pages, (E*)cq, (E*)c_pages, (E*)r_pages, gate, write_cache, status))
+                                stride, page_size, num_pages, (E*)cq, (E*)c_pages, (E*)r_pages, gate, write_cache, pairing, status))
   return q3::launch_status();
 }
 
 extern "C" int q3_latent_q_post(const void* q, int H, int dn, int rot, int dims, const float* freq, float mag,
-                                const int* positions, void* q_plain, void* q_rot, int dtype, int T, cudaStream_t stream) {
+                                const int* positions, void* q_plain, void* q_rot, int dtype, int T, int pairing,
+                                cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || dn <= 0 || rot < 0 || dims < 0 || dims > rot || dims % 2) return Q3_ERR_SIZE;
   if (dims > 8192) return Q3_ERR_SIZE;
   Q3_BY_DTYPE(dtype, q3::launch(q3::latent_q_post_kernel<E>, dim3(T), dim3(256), (size_t)dims * sizeof(float), stream,
-                                (const E*)q, H, dn, rot, dims, freq, mag, positions, (E*)q_plain, (E*)q_rot))
+                                (const E*)q, H, dn, rot, dims, freq, mag, positions, (E*)q_plain, (E*)q_rot, pairing))
   return q3::launch_status();
 }
 
 extern "C" int q3_latent_attn_ref(const float* q_abs, const void* q_rot, const void* c_pages, const void* r_pages,
                                   const int* positions, const int* tok_seq, const int* table, int stride, int page_size,
                                   int num_pages, void* out, int dtype, int T, int H, int rank, int rot, float scale,
-                                  int* status, cudaStream_t stream) {
+                                  const float* sink, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || rank <= 0 || rank > 32 * q3::LA_PER || rot < 0 || rot > 32 * q3::LA_ROT_PER || page_size <= 0 || stride <= 0)
     return Q3_ERR_SIZE;
@@ -254,7 +268,7 @@ extern "C" int q3_latent_attn_ref(const float* q_abs, const void* q_rot, const v
   if (blocks > 0x7fffffffll) return Q3_ERR_SIZE;
   Q3_BY_DTYPE(dtype, q3::launch(q3::latent_attn_ref_kernel<E>, dim3((unsigned)blocks), dim3(q3::LA_WARPS * 32), 0, stream,
                                 q_abs, (const E*)q_rot, (const E*)c_pages, (const E*)r_pages, positions, tok_seq, table,
-                                stride, page_size, num_pages, (E*)out, T, H, rank, rot, scale, status))
+                                stride, page_size, num_pages, (E*)out, T, H, rank, rot, scale, sink, status))
   return q3::launch_status();
 }
 

@@ -36,7 +36,7 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
                        const int* __restrict__ q_start, const int* __restrict__ kv_len, const int* __restrict__ table,
                        int stride, int page_size, int num_pages, __nv_bfloat16* __restrict__ out,
                        float* __restrict__ partial, int Ttot, int H, int rank, int rot, float scale_log2, int splits,
-                       int page_shift, int* status) {
+                       int page_shift, const float* __restrict__ sink, int* status) {
   constexpr int DKP = 64 * KS, PITCH = DKP + 8, BM = 16 * RG;
   extern __shared__ __align__(16) unsigned char lm_smem[];
   __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(lm_smem);                       // [2][LM_KT][PITCH]
@@ -237,7 +237,13 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
     if (!row_ok[r]) continue;
     const size_t row = (size_t)row_t[r] * H + row_h[r];
     if (splits == 1) {
-      const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+      float keep = 1.f;
+      if (sink) {  // one more term in the denominator: exp(sink), in the base-2 scale of the scores
+        const float s2 = sink[row_h[r]] * 1.4426950408889634f, m_new = fmaxf(m[r], s2);
+        keep = lm_exp2(m[r] - m_new);
+        l[r] = fmaf(l[r], keep, lm_exp2(s2 - m_new));
+      }
+      const float inv = l[r] > 0.f ? keep / l[r] : 0.f;
       __nv_bfloat16* dst = out + row * rank + w * NO * 16 + 2 * tid4;
 #pragma unroll
       for (int i = 0; i < 2 * NO; ++i)
@@ -260,7 +266,7 @@ latent_attn_mma_kernel(const float* __restrict__ q_abs, const __nv_bfloat16* __r
 constexpr int LM_MAX_SPLITS = 64;
 
 __global__ void latent_attn_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int rank,
-                                         int splits) {
+                                         int splits, const float* __restrict__ sink, int H) {
   __shared__ float weight[LM_MAX_SPLITS];
   pdl_wait();
   pdl_launch_dependents();
@@ -270,7 +276,9 @@ __global__ void latent_attn_merge_kernel(const float* __restrict__ partial, __nv
     float mx = -INFINITY;
     for (int s = threadIdx.x; s < splits; s += 32) mx = fmaxf(mx, p[(size_t)s * (rank + 2)]);
     mx = warp_max(mx);
-    float total = 0.f;  // every lane adds all ranges in their order: the same sum in every lane
+    const float s2 = sink ? sink[row % H] * 1.4426950408889634f : -INFINITY;  // the sink, a range without keys
+    mx = fmaxf(mx, s2);
+    float total = sink ? lm_exp2(s2 - mx) : 0.f;  // every lane adds all ranges in their order: the same sum in every lane
     for (int s = 0; s < splits; ++s) {
       const float ms = p[(size_t)s * (rank + 2)];
       if (ms != -INFINITY) total += p[(size_t)s * (rank + 2) + 1] * lm_exp2(ms - mx);
@@ -293,7 +301,7 @@ template <int KS, int NO, int RG>
 static int lm_launch(const float* q_abs, const void* q_rot, const void* c_pages, const void* r_pages, const int* q_start,
                      const int* kv_len, const int* table, int stride, int page_size, int num_pages, void* out,
                      float* partial, int T, int B, int max_q_len, int H, int rank, int rot, float scale, int splits,
-                     int* status, cudaStream_t stream) {
+                     const float* sink, int* status, cudaStream_t stream) {
   using bf16 = __nv_bfloat16;
   constexpr int PITCH = 64 * KS + 8, LM_KT = RG == 2 ? 32 : 16;
   const size_t smem = (size_t)2 * LM_KT * PITCH * sizeof(bf16) + (size_t)RG * 4 * 16 * LM_KT * sizeof(float);
@@ -307,11 +315,11 @@ static int lm_launch(const float* q_abs, const void* q_rot, const void* c_pages,
   launch(latent_attn_mma_kernel<KS, NO, RG, RG == 2 ? 32 : 16>, dim3(B, (unsigned)tiles, splits), dim3(RG * 128), smem, stream, q_abs,
          (const bf16*)q_rot, (const bf16*)c_pages, (const bf16*)r_pages, q_start, kv_len, table, stride, page_size,
          num_pages, (bf16*)out, partial, T, H, rank, rot, scale * 1.4426950408889634f, splits, page_shift_of(page_size),
-         status);
+         sink, status);
   if (splits > 1) {
     g_launch_early = false;  // started after every range has left its result
     launch(latent_attn_merge_kernel, dim3((unsigned)((size_t)T * H)), dim3(128), 0, stream, (const float*)partial,
-           (bf16*)out, rank, splits);
+           (bf16*)out, rank, splits, sink, H);
     g_launch_early = true;
   }
   return launch_status();
@@ -337,7 +345,7 @@ extern "C" int q3_latent_attn_mma_takes(int rank, int rot) {
 extern "C" int q3_latent_attn_mma(const float* q_abs, const void* q_rot, const void* c_pages, const void* r_pages,
                                   const int* q_start, const int* kv_len, const int* table, int stride, int page_size,
                                   int num_pages, void* out, float* partial, int T, int B, int max_q_len, int H, int rank,
-                                  int rot, float scale, int splits, int* status, cudaStream_t stream) {
+                                  int rot, float scale, int splits, const float* sink, int* status, cudaStream_t stream) {
   if (T <= 0 || B <= 0) return 0;
   if (!q3_latent_attn_mma_takes(rank, rot) || H <= 0 || max_q_len <= 0 || page_size <= 0 || stride <= 0 || splits < 1)
     return Q3_ERR_SIZE;
@@ -348,11 +356,11 @@ extern "C" int q3_latent_attn_mma(const float* q_abs, const void* q_rot, const v
   const bool wide = (long long)max_q_len * H > 16;  // more than one row group's rows per request
 #define Q3_LM(KS, NO)                                                                                                  \
   return wide ? q3::lm_launch<KS, NO, 2>(q_abs, q_rot, c_pages, r_pages, q_start, kv_len, table, stride, page_size,    \
-                                         num_pages, out, partial, T, B, max_q_len, H, rank, rot, scale, splits, status, \
-                                         stream)                                                                       \
+                                         num_pages, out, partial, T, B, max_q_len, H, rank, rot, scale, splits, sink,  \
+                                         status, stream)                                                               \
               : q3::lm_launch<KS, NO, 1>(q_abs, q_rot, c_pages, r_pages, q_start, kv_len, table, stride, page_size,    \
-                                         num_pages, out, partial, T, B, max_q_len, H, rank, rot, scale, splits, status, \
-                                         stream);
+                                         num_pages, out, partial, T, B, max_q_len, H, rank, rot, scale, splits, sink,  \
+                                         status, stream);
   if (rank == 512) { Q3_LM(9, 8) }
   if (rank == 256) { Q3_LM(5, 4) }
   if (rank == 128) { Q3_LM(3, 2) }

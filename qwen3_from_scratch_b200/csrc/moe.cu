@@ -9,6 +9,11 @@
 //   moe_pair_down  out[t] = base[t] + sum_k weight[t, k] W_down[e_k] a[t, k]: a warp per output value, the chosen
 //                  experts in the order the router listed them.
 //
+// Gated experts (`gate_block` > 0): W_down (act(W_gate h) * (W_up h)); the stack `up` then holds 2 F rows per
+// expert, gate and up rows alternating in blocks of `gate_block` rows (gate_block = F: all gate rows, then all up
+// rows).  `in_wts` (or null): the router's weight multiplies what the expert reads (both of its first products)
+// instead of what it returns; the caller then passes ones as `wts` to the second kernel.
+//
 // Sums over a row are taken lane by lane in ascending order and then across the warp, so a token's result does not
 // depend on the batch.  The expert weights are stacked: up [E, F, W], down [E, W, F].
 #include "common.cuh"
@@ -85,7 +90,8 @@ __global__ void moe_route_kernel(const T* __restrict__ h, const float* __restric
 // grid (pairs, ceil(F / warps)).  a[pair, f] = act(sum_i up[e, f, i] h[t, i]), t = pair / top.
 template <typename T>
 __global__ void moe_pair_up_kernel(const T* __restrict__ h, const T* __restrict__ up, const int* __restrict__ ids,
-                                   T* __restrict__ a, int W, int F, int E, int top, int act) {
+                                   T* __restrict__ a, int W, int F, int E, int top, int act, int gate_block,
+                                   const float* __restrict__ in_wts) {
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -98,10 +104,26 @@ __global__ void moe_pair_up_kernel(const T* __restrict__ h, const T* __restrict_
     return;
   }
   const T* row = h + (size_t)(pair / top) * W;
+  const float in_scale = in_wts ? in_wts[pair] : 1.f;
+  if (gate_block > 0) {
+    const size_t gate_row = (size_t)(f / gate_block) * 2 * gate_block + f % gate_block;
+    const T* wg = up + ((size_t)e * 2 * F + gate_row) * W;
+    const T* wu = wg + (size_t)gate_block * W;
+    float dg = 0.f, du = 0.f;
+    for (int i = lane; i < W; i += 32) {
+      const float x = to_float(row[i]);
+      dg = fmaf(x, to_float(wg[i]), dg);
+      du = fmaf(x, to_float(wu[i]), du);
+    }
+    dg = warp_sum(dg) * in_scale;
+    du = warp_sum(du) * in_scale;
+    if (lane == 0) a[(size_t)pair * F + f] = from_float<T>(activate(dg, act) * du);
+    return;
+  }
   const T* w = up + ((size_t)e * F + f) * W;
   float dot = 0.f;
   for (int i = lane; i < W; i += 32) dot = fmaf(to_float(row[i]), to_float(w[i]), dot);
-  dot = warp_sum(dot);
+  dot = warp_sum(dot) * in_scale;
   if (lane == 0) a[(size_t)pair * F + f] = from_float<T>(activate(dot, act));
 }
 
@@ -148,15 +170,17 @@ extern "C" int q3_moe_route(const void* h, const float* wr, const float* bias, i
 }
 
 // a: [T * top, F] = act(up[ids] h); out: [T, W] = base + sum_k wts down[ids] a.  act: a Q3_ACT_* code.
+// gate_block > 0: gated experts (see the head of the file); in_wts: float32 [T * top] or null.
 extern "C" int q3_moe_pairs(const void* h, const void* up, const void* down, const int* ids, const float* wts,
                             const void* base, void* a, void* out, int dtype, int T, int W, int F, int E, int top, int act,
-                            cudaStream_t stream) {
+                            int gate_block, const float* in_wts, cudaStream_t stream) {
+  if (gate_block < 0 || (gate_block > 0 && F % gate_block)) return Q3_ERR_SIZE;
   if (T <= 0) return 0;
   if (W <= 0 || F <= 0 || E <= 0 || top <= 0 || (long long)T * top > 0x7fffffffll || F > 4 * 65535 || W > 4 * 65535 || act < 0 || act > Q3_ACT_RELU_SQ)
     return Q3_ERR_SIZE;
   const int warps = 4;
   Q3_BY_DTYPE(dtype, q3::launch(q3::moe_pair_up_kernel<E_>, dim3(T * top, (F + warps - 1) / warps), dim3(warps * 32), 0,
-                                stream, (const E_*)h, (const E_*)up, ids, (E_*)a, W, F, E, top, act))
+                                stream, (const E_*)h, (const E_*)up, ids, (E_*)a, W, F, E, top, act, gate_block, in_wts))
   int code = q3::launch_status();
   if (code) return code;
   Q3_BY_DTYPE(dtype, q3::launch(q3::moe_pair_down_kernel<E_>, dim3(T, (W + warps - 1) / warps), dim3(warps * 32), 0, stream,

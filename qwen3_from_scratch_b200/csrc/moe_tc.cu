@@ -7,11 +7,14 @@
 //                   of range), src[row] (the row's pair, -1 for padding) and meta = {tiles in use, expert of tile 0,
 //                   expert of tile 1, ...}.  Which row of its expert a pair gets is not fixed from run to run; a
 //                   row's product does not depend on where in a tile it lies.
-//   moe_gather      row r of the sorted input = the token's row of h (zeros for padding).
+//   moe_gather      row r of the sorted input = the token's row of h (zeros for padding), times the pair's router
+//                   weight where that weight belongs to what the expert reads (`in_wts`).
 //   moe_grouped     the persistent kernel of gemm_tc.cu (TMA loader, one tcgen05.mma thread, accumulators in tensor
 //                   memory, epilogue warps) over the tiles that `meta` lists: the tile's rows of W start at
 //                   expert * N.  The number of tiles is read on the device, so a step's launches do not depend on
-//                   the routing and a captured graph replays them.  The epilogue applies the activation.
+//                   the routing and a captured graph replays them.  The epilogue applies the activation; for gated
+//                   experts (gate and up rows alternating in blocks of 16 rows of a stack of 2 F) it multiplies the
+//                   activated gate columns of a 32-column piece by the piece's up columns and stores 16 values.
 //   moe_combine     out[t] = base[t] + sum_k weight[t, k] y[pos[t, k]], float32 sums in the router's order.
 //
 // Every wait on an mbarrier is bounded as in gemm_tc.cu: a wait that runs out sets the TIMEOUT bit of the status word,
@@ -80,7 +83,8 @@ moe_sort_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__
 
 // grid (rows): eight values per thread and turn.  W a multiple of 8, rows 16-byte aligned.
 __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ h, const int* __restrict__ src,
-                                  const int* __restrict__ meta, __nv_bfloat16* __restrict__ sorted, int W, int top) {
+                                  const int* __restrict__ meta, __nv_bfloat16* __restrict__ sorted, int W, int top,
+                                  const float* __restrict__ in_wts) {
   pdl_wait();
   pdl_launch_dependents();
   const int r = blockIdx.x;
@@ -88,7 +92,21 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ h, const int
   const int p = src[r];
   const uint4* from = p >= 0 ? reinterpret_cast<const uint4*>(h + (size_t)(p / top) * W) : nullptr;
   uint4* to = reinterpret_cast<uint4*>(sorted + (size_t)r * W);
-  for (int i = threadIdx.x; i < W / 8; i += blockDim.x) to[i] = from ? from[i] : make_uint4(0, 0, 0, 0);
+  if (!from || !in_wts) {
+    for (int i = threadIdx.x; i < W / 8; i += blockDim.x) to[i] = from ? from[i] : make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const float w = in_wts[p];  // the expert reads the row times its weight, rounded once
+  for (int i = threadIdx.x; i < W / 8; i += blockDim.x) {
+    uint4 v = from[i];
+    __nv_bfloat162* v2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __bfloat1622float2(v2[j]);
+      v2[j] = __floats2bfloat162_rn(f.x * w, f.y * w);
+    }
+    to[i] = v;
+  }
 }
 
 // grid (tokens).  y: the sorted rows of the second product.
@@ -134,9 +152,28 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* __restrict__ y, const in
   }
 }
 
+constexpr int MOE_GATED = 0x100;  // OR-ed into the activation code: the columns are gate and up in blocks of 16
+
 // 32 columns of one row: activation, rounding to bfloat16, store.
 __device__ __forceinline__ void moe_store_chunk(const uint32_t (&v)[32], __nv_bfloat16* C, int row, int col0, int N, int ldc,
                                                 int act) {
+  if (act & MOE_GATED) {  // columns col0 .. +15: gates, +16 .. +31: their up values; N = 2 ldc-columns, whole pieces
+    if (col0 + 32 > N) return;
+    __nv_bfloat16* dst = C + (size_t)row * ldc + (col0 >> 1);
+    float g[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) g[j] = activate(__uint_as_float(v[j]), act & 0xff) * __uint_as_float(v[16 + j]);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      uint4 pk;
+      pk.x = pack2(__float_as_uint(g[8 * j + 0]), __float_as_uint(g[8 * j + 1]));
+      pk.y = pack2(__float_as_uint(g[8 * j + 2]), __float_as_uint(g[8 * j + 3]));
+      pk.z = pack2(__float_as_uint(g[8 * j + 4]), __float_as_uint(g[8 * j + 5]));
+      pk.w = pack2(__float_as_uint(g[8 * j + 6]), __float_as_uint(g[8 * j + 7]));
+      reinterpret_cast<uint4*>(dst)[j] = pk;
+    }
+    return;
+  }
   __nv_bfloat16* dst = C + (size_t)row * ldc + col0;
   float r[32];
 #pragma unroll
@@ -344,16 +381,19 @@ static int moe_grouped_launch(const void* A, const void* W, void* C, const int* 
 extern "C" int q3_moe_tile_rows() { return q3::MOE_BM; }
 
 // The routed experts of T tokens (bfloat16) by sorted rows and two grouped products.  h: [T, W]; up: [E, F, W];
+// (gated: [E, 2 F, W], gate and up rows alternating in blocks of 16, F a multiple of 16); in_wts: [T, top] or null, the
+// weights of what the experts read (`wts` are those of what they return);
 // down: [E, W, F]; ids, wts: [T, top]; base: [T, W] or null; out: [T, W].  Scratch for max_tiles >= T * top / 128 + E
 // tiles: sorted_in [max_tiles * 128, W], sorted_act [.., F], sorted_out [.., W], pos int32 [T * top], src int32
 // [max_tiles * 128], meta int32 [1 + max_tiles].  W and F multiples of 8, all bases 16-byte aligned.
 extern "C" int q3_moe_grouped(const void* h, const void* up, const void* down, const int* ids, const float* wts,
                               const void* base, void* out, void* sorted_in, void* sorted_act, void* sorted_out, int* pos,
-                              int* src, int* meta, int T, int W, int F, int E, int top, int max_tiles, int act, int* status,
-                              cudaStream_t stream) {
+                              int* src, int* meta, int T, int W, int F, int E, int top, int max_tiles, int act, int gated,
+                              const float* in_wts, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
+  if (gated && F % 16) return Q3_ERR_SIZE;
   if (W <= 0 || F <= 0 || E <= 0 || E > 4096 || top <= 0 || W % 8 || F % 8 || (long long)T * top > 0x3fffffffll ||
-      max_tiles < (int)(((long long)T * top) / q3::MOE_BM) + E || (long long)E * (W > F ? W : F) > 0x7fffffffll ||
+      max_tiles < (int)(((long long)T * top) / q3::MOE_BM) + E || (long long)E * (W > 2 * F ? W : 2 * F) > 0x7fffffffll ||
       act < 0 || act > Q3_ACT_RELU_SQ)
     return Q3_ERR_SIZE;
   if ((uintptr_t)h % 16 || (uintptr_t)up % 16 || (uintptr_t)down % 16 || (uintptr_t)out % 16 || (uintptr_t)sorted_in % 16 ||
@@ -366,7 +406,7 @@ extern "C" int q3_moe_grouped(const void* h, const void* up, const void* down, c
   q3::launch(q3::moe_sort_kernel, dim3(1), dim3(1024), (size_t)2 * E * sizeof(int), stream, ids, pairs, E, pos, src, meta,
              max_tiles);
   q3::launch(q3::moe_gather_kernel, dim3(max_tiles * q3::MOE_BM), dim3(128), 0, stream, (const bf16*)h, (const int*)src,
-             (const int*)meta, (bf16*)sorted_in, W, top);
+             (const int*)meta, (bf16*)sorted_in, W, top, in_wts);
   int code = q3::launch_status();
   if (code) return code;
   // the tile width that needs fewer rounds of the SMs for the tiles to expect (half of the padding tiles in use)
@@ -376,13 +416,14 @@ extern "C" int q3_moe_grouped(const void* h, const void* up, const void* down, c
     const long long t256 = expect * ((n + 255) / 256), t128 = expect * ((n + 127) / 128);
     return ((t256 + sms - 1) / sms) * 256 <= ((t128 + sms - 1) / sms) * 128;
   };
-  auto product = [&](const void* a, const void* wgt, void* c, int n, int k, int activation) {
-    return wide(n) ? q3::moe_grouped_launch<256>(a, wgt, c, meta, map_tiles, max_tiles, n, k, E, n, activation, status, stream)
-                   : q3::moe_grouped_launch<128>(a, wgt, c, meta, map_tiles, max_tiles, n, k, E, n, activation, status, stream);
+  auto product = [&](const void* a, const void* wgt, void* c, int n, int k, int ldc, int activation) {
+    return wide(n) ? q3::moe_grouped_launch<256>(a, wgt, c, meta, map_tiles, max_tiles, n, k, E, ldc, activation, status, stream)
+                   : q3::moe_grouped_launch<128>(a, wgt, c, meta, map_tiles, max_tiles, n, k, E, ldc, activation, status, stream);
   };
-  code = product(sorted_in, up, sorted_act, F, W, act);
+  code = gated ? product(sorted_in, up, sorted_act, 2 * F, W, F, act | q3::MOE_GATED)
+               : product(sorted_in, up, sorted_act, F, W, F, act);
   if (code) return code;
-  code = product(sorted_act, down, sorted_out, W, F, Q3_ACT_NONE);
+  code = product(sorted_act, down, sorted_out, W, F, W, Q3_ACT_NONE);
   if (code) return code;
   q3::launch(q3::moe_combine_kernel, dim3(T), dim3(128), 0, stream, (const bf16*)sorted_out, (const int*)pos, wts,
              (const bf16*)base, (bf16*)out, W, top);

@@ -51,15 +51,17 @@ __global__ void pw_qkv_post_kernel(const T* __restrict__ proj, int ld, int k_col
     const float v = to_float(row[k_col + i]);
     ssk = fmaf(v, v, ssk);
   }
-  const float rq = 1.0f / sqrtf(block_sum(ssq, red) / (float)(H * D) + eps);
-  const float rk = 1.0f / sqrtf(block_sum(ssk, red) / (float)(G * D) + eps);  // block_sum's barriers also publish cs
+  // without norm weights (wq null) q and k pass as projected; block_sum's barriers also publish cs
+  const float rq = wq ? 1.0f / sqrtf(block_sum(ssq, red) / (float)(H * D) + eps) : 1.0f;
+  const float rk = wq ? 1.0f / sqrtf(block_sum(ssk, red) / (float)(G * D) + eps) : 1.0f;
+  if (!wq) __syncthreads();
   for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
     const int d = i % D;
-    float v = to_float(row[i]) * rq * wq[i];
+    float v = wq ? to_float(row[i]) * rq * wq[i] : to_float(row[i]);
     if (d < dims) {
       const int p = d < half ? d : d - half;
       const int o = d < half ? i + half : i - half;
-      const float u = to_float(row[o]) * rq * wq[o];
+      const float u = wq ? to_float(row[o]) * rq * wq[o] : to_float(row[o]);
       v = d < half ? v * cs[p] - u * cs[half + p] : v * cs[p] + u * cs[half + p];
     }
     q_out[(size_t)t * H * D + i] = from_float<T>(v);
@@ -77,11 +79,11 @@ __global__ void pw_qkv_post_kernel(const T* __restrict__ proj, int ld, int k_col
   const int in_page = pos % page_size;
   for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
     const int g = i / D, d = i - g * D;
-    float v = to_float(row[k_col + i]) * rk * wk[i];
+    float v = wk ? to_float(row[k_col + i]) * rk * wk[i] : to_float(row[k_col + i]);
     if (d < dims) {
       const int p = d < half ? d : d - half;
       const int o = d < half ? i + half : i - half;
-      const float u = to_float(row[k_col + o]) * rk * wk[o];
+      const float u = wk ? to_float(row[k_col + o]) * rk * wk[o] : to_float(row[k_col + o]);
       v = d < half ? v * cs[p] - u * cs[half + p] : v * cs[p] + u * cs[half + p];
     }
     k_pages[(((size_t)page * G + g) * page_size + in_page) * D + d] = from_float<T>(v);
@@ -159,7 +161,7 @@ pw_attn_ref_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const
                    const int* __restrict__ tok_seq, const int* __restrict__ table, int stride, int num_pages,
                    const int* __restrict__ ptable, int pstride, int num_ppages, int page_size, T* __restrict__ out, int ldo,
                    int Ttot, int H, int G, int D, int Dv, int window, int P, float scale, float cap, float out_scale,
-                   int* status) {
+                   int block_limit, int* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -183,7 +185,7 @@ pw_attn_ref_kernel(const T* __restrict__ q, const T* __restrict__ k_pages, const
   }
   float m = -INFINITY, l = 0.f;
   const int first = max(0, pos - window + 1);
-  const int blocks = first / P;  // the blocks that end before the window
+  const int blocks = min(first / P, block_limit);  // the blocks that end before the window, the first so many of them
   const int* prow = ptable + (size_t)b * pstride;
   const int* row = table + (size_t)b * stride;
   const int total = blocks + (pos - first + 1);
@@ -262,11 +264,13 @@ extern "C" int q3_pool_blocks(const void* k_pages, const void* v_pages, void* pk
 }
 
 // q: [T, H, D]; out: rows of `ldo` values, head h at column h * Dv, multiplied by out_scale.  cap <= 0: no cap.
+// block_limit: only the first so many blocks are ever read (negative: all).  With P = 1 and the token pages given as
+// the block pages too, that is a window that also keeps a request's first `block_limit` tokens.
 extern "C" int q3_pw_attn_ref(const void* q, const void* k_pages, const void* v_pages, const void* pk_pages,
                               const void* pv_pages, const int* positions, const int* tok_seq, const int* table, int stride,
                               int num_pages, const int* ptable, int pstride, int num_ppages, int page_size, void* out,
                               int ldo, int dtype, int T, int H, int G, int D, int Dv, int window, int P, float scale,
-                              float cap, float out_scale, int* status, cudaStream_t stream) {
+                              float cap, float out_scale, int block_limit, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || D <= 0 || D > 32 * q3::PW_PER || Dv <= 0 || Dv > 32 * q3::PW_PER || window <= 0 ||
       P <= 0 || page_size <= 0 || stride <= 0 || pstride <= 0)
@@ -276,6 +280,7 @@ extern "C" int q3_pw_attn_ref(const void* q, const void* k_pages, const void* v_
   Q3_BY_DTYPE(dtype, q3::launch(q3::pw_attn_ref_kernel<E>, dim3((unsigned)blocks), dim3(128), 0, stream, (const E*)q,
                                 (const E*)k_pages, (const E*)v_pages, (const E*)pk_pages, (const E*)pv_pages, positions,
                                 tok_seq, table, stride, num_pages, ptable, pstride, num_ppages, page_size, (E*)out, ldo, T,
-                                H, G, D, Dv, window, P, scale, cap, out_scale, status))
+                                H, G, D, Dv, window, P, scale, cap, out_scale, block_limit < 0 ? 0x7fffffff : block_limit,
+                                status))
   return q3::launch_status();
 }

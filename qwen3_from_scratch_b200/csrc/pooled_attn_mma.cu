@@ -44,7 +44,8 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ q_start, const int* __restrict__ kv_len, const int* __restrict__ block_table,
                    int table_stride, int num_pages, const int* __restrict__ pooled_table, int ptable_stride,
                    int num_ppages, int page_size, int Hq, int Hkv, float scale, float cap, float out_scale, int window,
-                   int P, int splits, int T_total, float* __restrict__ part_o, float* __restrict__ part_ml, int* status) {
+                   int P, int block_limit, int splits, int T_total, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, int* status) {
   pdl_wait();
   pdl_launch_dependents();
   using S = PwShape<KT, VT, DEC>;
@@ -76,7 +77,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const int last_row = min(total_rows, row0 + BM) - 1;
   const int pos_first = past + row0 / g, pos_last = past + last_row / g;
   const int lo_key = max(0, pos_first - window + 1);
-  const int blocks_hi = max(0, pos_last - window + 1) / P;  // blocks the newest row reads
+  const int blocks_hi = min(max(0, pos_last - window + 1) / P, block_limit);  // blocks the newest row reads
   const int ptiles = (blocks_hi + PWM_BN - 1) / PWM_BN;
   const int tile_lo = lo_key / PWM_BN, tile_hi = pos_last / PWM_BN;
   const int tiles = ptiles + tile_hi - tile_lo + 1;
@@ -130,7 +131,7 @@ pw_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     const int R = row0 + wrow + gid + 8 * r;
     row_pos[r] = R < total_rows ? past + R / g : pos_last;  // rows past the end compute something finite, unused
     row_lo[r] = max(0, row_pos[r] - window + 1);
-    row_blocks[r] = row_lo[r] / P;
+    row_blocks[r] = min(row_lo[r] / P, block_limit);
   }
 
   float o[2 * VT][4];
@@ -330,8 +331,8 @@ static int pw_attn_mma_launch(const void* q, const void* k_pages, const void* v_
                               const void* pv_pages, void* out, int ldo, const int* q_start, const int* kv_len,
                               const int* table, int stride, int num_pages, const int* ptable, int pstride, int num_ppages,
                               int page_size, int B, int max_q_len, int Hq, int Hkv, float scale, float cap, float out_scale,
-                              int window, int P, int T_total, float* part_o, float* part_ml, long long part_rows,
-                              int* status, cudaStream_t stream) {
+                              int window, int P, int block_limit, int T_total, float* part_o, float* part_ml,
+                              long long part_rows, int* status, cudaStream_t stream) {
   using S = PwShape<KT, VT, DEC>;
   static bool configured = false;
   if (!configured) {
@@ -356,8 +357,8 @@ static int pw_attn_mma_launch(const void* q, const void* k_pages, const void* v_
   q3::launch(pw_attn_mma_kernel<KT, VT, DEC>, dim3((unsigned)tiles, Hkv, B * splits), dim3(S::WARPS * 32), S::SMEM_BYTES, stream,
              (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages,
              (const __nv_bfloat16*)pk_pages, (const __nv_bfloat16*)pv_pages, (__nv_bfloat16*)out, ldo, q_start, kv_len, table,
-             stride, num_pages, ptable, pstride, num_ppages, page_size, Hq, Hkv, scale, cap, out_scale, window, P, splits,
-             T_total, part_o, part_ml, status);
+             stride, num_pages, ptable, pstride, num_ppages, page_size, Hq, Hkv, scale, cap, out_scale, window, P, block_limit,
+             splits, T_total, part_o, part_ml, status);
   if (splits > 1)
     q3::launch(pw_attn_merge_kernel, dim3(T_total, Hq), dim3(S::DV < 128 ? S::DV : 128), 0, stream, (const float*)part_o,
                (const float*)part_ml, (__nv_bfloat16*)out, ldo, T_total, Hq, S::DV, splits, out_scale);
@@ -375,13 +376,14 @@ extern "C" int q3_pw_attn_mma_takes(int D, int Dv) {
 // q: bf16 [T, Hq, D]; token pages k [pages, Hkv, page, D], v [.., Dv]; block pages pk, pv alike; out: rows of `ldo`
 // values, head h at column h * Dv, times out_scale.  cap <= 0: no cap.  part_o (float32, part_rows * Dv values) and part_ml
 // (float32, part_rows * 2 values), or null: scratch for a step of T tokens whose keys are cut into ranges (part_rows /
-// (T * Hq) of them at most).
+// (T * Hq) of them at most).  block_limit: only the first so many blocks are ever read (negative: all).
 extern "C" int q3_pw_attn_mma(const void* q, const void* k_pages, const void* v_pages, const void* pk_pages,
                               const void* pv_pages, void* out, int ldo, const int* q_start, const int* kv_len,
                               const int* table, int stride, int num_pages, const int* ptable, int pstride, int num_ppages,
                               int page_size, int B, int max_q_len, int Hq, int Hkv, int D, int Dv, float scale, float cap,
-                              float out_scale, int window, int P, int T, float* part_o, float* part_ml, long long part_rows,
-                              int* status, cudaStream_t stream) {
+                              float out_scale, int window, int P, int block_limit, int T, float* part_o, float* part_ml,
+                              long long part_rows, int* status, cudaStream_t stream) {
+  if (block_limit < 0) block_limit = 0x7fffffff;  // all blocks
   if (B <= 0 || max_q_len <= 0) return 0;
   if (Hkv <= 0 || Hq % Hkv || !q3_pw_attn_mma_takes(D, Dv) || page_size <= 0 || stride <= 0 || pstride <= 0 || B > 65535 ||
       Hkv > 65535 || window <= 0 || P <= 0 || ldo % 2)
@@ -394,11 +396,11 @@ extern "C" int q3_pw_attn_mma(const void* q, const void* k_pages, const void* v_
     if ((long long)max_q_len * (Hq / Hkv) <= 16)                                                                        \
       return q3::pw_attn_mma_launch<KT, VT, true>(q, k_pages, v_pages, pk_pages, pv_pages, out, ldo, q_start, kv_len,   \
                                                   table, stride, num_pages, ptable, pstride, num_ppages, page_size, B,  \
-                                                  max_q_len, Hq, Hkv, scale, cap, out_scale, window, P, T, part_o,      \
+                                                  max_q_len, Hq, Hkv, scale, cap, out_scale, window, P, block_limit, T, part_o, \
                                                   part_ml, part_rows, status, stream);                                  \
     return q3::pw_attn_mma_launch<KT, VT, false>(q, k_pages, v_pages, pk_pages, pv_pages, out, ldo, q_start, kv_len,    \
                                                  table, stride, num_pages, ptable, pstride, num_ppages, page_size, B,   \
-                                                 max_q_len, Hq, Hkv, scale, cap, out_scale, window, P, T, part_o,       \
+                                                 max_q_len, Hq, Hkv, scale, cap, out_scale, window, P, block_limit, T, part_o, \
                                                  part_ml, part_rows, status, stream);                                   \
   }
   Q3_PW_CASE(2, 2) Q3_PW_CASE(2, 4) Q3_PW_CASE(2, 8) Q3_PW_CASE(4, 2) Q3_PW_CASE(4, 4) Q3_PW_CASE(4, 8) Q3_PW_CASE(8, 2)

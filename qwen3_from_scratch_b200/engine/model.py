@@ -15,7 +15,8 @@ import torch
 from ..cache.manager import CacheLayout, layout_of
 from ..config.model_config import ModelConfig
 from ..kernels import ops
-from ..parts.base import EMBEDDING_OUTPUT, NEXT_NORM_WEIGHT, STREAM_SUMSQ, ModelSpec, Runtime, StepContext
+from ..parts.base import (EMBEDDING_OUTPUT, EMBEDDING_SIDE, LAYER_REPEAT, NEXT_NORM_WEIGHT, STREAM_SUMSQ, ModelSpec, Runtime,
+                          StepContext)
 from ..registry import build_model_spec, create_part, load_config
 from ..weights.loader import load_weights
 from ..weights.random_init import random_weights_on_device
@@ -98,6 +99,8 @@ class Model:
                                   dtype=stream.dtype)[: stream.shape[0]]
             kept.copy_(stream)
             ctx.per_step[EMBEDDING_OUTPUT] = kept
+        if getattr(self.embedding, "has_side_table", False):  # a second table of the token, read by the layers
+            ctx.per_step[EMBEDDING_SIDE] = self.embedding.side_rows(ctx.token_ids)
         pending = None
         order = self.spec.order
         for i, call in enumerate(order):
@@ -105,6 +108,7 @@ class Model:
             # the weight of the norm that reads the stream after this layer, for layers that prepare the stream for it
             nxt = self.layers[order[i + 1].layer] if i + 1 < len(order) else None
             ctx.per_step[NEXT_NORM_WEIGHT] = getattr(nxt, "first_norm_weight", None)
+            ctx.per_step[LAYER_REPEAT] = call.repeat
             pending = layer.forward(stream, pending, ctx, call.cache, call.write_cache)
             if not layer.keeps_stream_stats:
                 ctx.per_step.pop(STREAM_SUMSQ, None)  # whatever it did to the stream, the sums describe it no longer

@@ -124,14 +124,15 @@ _SIGNATURES = {
     "q3_act": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_int, _c_void_p],
     "q3_latent_kv_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
                           _c_float, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
-                          _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+                          _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "q3_latent_q_post": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_void_p,
-                         _c_int, _c_int, _c_void_p],
+                         _c_int, _c_int, _c_int, _c_void_p],
     "q3_latent_attn_ref": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
-                           _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
+                           _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p,
+                           _c_void_p],
     "q3_latent_attn_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                            _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
-                           _c_void_p, _c_void_p],
+                           _c_void_p, _c_void_p, _c_void_p],
     "q3_gate_heads": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_ssd_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                     _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -156,23 +157,33 @@ _SIGNATURES = {
                        _c_void_p, _c_void_p],
     "q3_pw_attn_ref": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
                        _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                       _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_void_p, _c_void_p],
+                       _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_void_p, _c_void_p],
     "q3_pw_attn_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                       _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_ll,
-                       _c_void_p, _c_void_p],
+                       _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                       _c_ll, _c_void_p, _c_void_p],
     "q3_mingru_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_void_p],
     "q3_moe_grouped": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                       _c_void_p, _c_void_p],
+                       _c_int, _c_void_p, _c_void_p, _c_void_p],
     "q3_mingru_scan_chunked": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                                _c_float, _c_void_p, _c_void_p],
     "q3_moe_route": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                      _c_float, _c_void_p],
     "q3_moe_pairs": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
-                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "q3_add_dyt": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                   _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_side_gate": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_add_unit_rms": [_c_void_p, _c_void_p, _c_void_p, _c_float, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_sigmoid_gate": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "q3_mlstm_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p,
+                      _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
+                      _c_void_p, _c_void_p],
+    "q3_mlstm_out": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_float, _c_float, _c_void_p, _c_int, _c_int, _c_int,
+                     _c_int, _c_int, _c_void_p],
 }
 
 
@@ -218,6 +229,8 @@ def library() -> ctypes.CDLL:
                 lib.q3_scan_chunk.restype = _c_int
                 lib.q3_mingru_chunk.argtypes = []
                 lib.q3_mingru_chunk.restype = _c_int
+                lib.q3_mlstm_max_dim.argtypes = []
+                lib.q3_mlstm_max_dim.restype = _c_int
                 lib.q3_moe_tile_rows.argtypes = []
                 lib.q3_moe_tile_rows.restype = _c_int
                 lib.q3_sample_scratch_bytes.argtypes = [_c_int]
@@ -1430,44 +1443,57 @@ def act(x: torch.Tensor, out: torch.Tensor, activation: str) -> None:
 
 
 # ------------------------------------------------------------------ attention through a latent
+ROTARY_PAIRINGS = {"halves": 0, "neighbours": 1}  # which values of a vector turn together
+
+
+def rotary_pairing(name: str) -> int:
+    if name not in ROTARY_PAIRINGS:
+        raise KernelError(f"unknown pairing '{name}' of a rotation (known: {', '.join(ROTARY_PAIRINGS)})")
+    return ROTARY_PAIRINGS[name]
+
+
 def latent_kv_post(proj: torch.Tensor, q_rank: int, kv_col: int, rank: int, rot: int, dims: int, gate_col: int, heads: int,
                    q_norm: torch.Tensor, kv_norm: torch.Tensor, eps: float, freq: torch.Tensor, magnitude: float,
                    positions: torch.Tensor, tok_seq: torch.Tensor, table: torch.Tensor, c_pages: torch.Tensor,
-                   r_pages: torch.Tensor, cq: torch.Tensor, gate: torch.Tensor, write_cache: bool,
-                   status: torch.Tensor) -> None:
+                   r_pages: torch.Tensor, cq: torch.Tensor, gate: Optional[torch.Tensor], write_cache: bool,
+                   status: torch.Tensor, pairing: str = "halves") -> None:
     """From one product ``proj`` [T, ld] (query latent at column 0, kv latent and shared key part from ``kv_col``,
     gate pre-activations from ``gate_col``): cq = rmsnorm(query latent) * q_norm; the normed kv latent and the key part
     rotated by position into the pages ``c_pages`` [pages, 1, page, rank] and ``r_pages`` [pages, 1, page, rot];
-    gate [T, heads] = sigmoid (float32).  The first ``dims`` values of the key part are rotated (pairs i, i + dims / 2,
-    angle position * freq[i], sine and cosine times ``magnitude``)."""
+    gate [T, heads] = sigmoid (float32; None: the mixer has no gates).  The first ``dims`` values of the key part are
+    rotated (``pairing`` "halves": pairs i, i + dims / 2; "neighbours": pairs 2i, 2i + 1; angle position * freq[i], sine
+    and cosine times ``magnitude``)."""
     _check("latent_kv_post.proj", proj)
     _check("latent_kv_post.cq", cq, proj.dtype)
     _check("latent_kv_post.c_pages", c_pages, proj.dtype)
     _check("latent_kv_post.r_pages", r_pages, proj.dtype)
-    _check("latent_kv_post.gate", gate, torch.float32)
+    if gate is not None:
+        _check("latent_kv_post.gate", gate, torch.float32)
     for name, t in (("q_norm", q_norm), ("kv_norm", kv_norm), ("freq", freq)):
         _check(f"latent_kv_post.{name}", t, torch.float32)
     for name, t in (("positions", positions), ("tok_seq", tok_seq), ("table", table)):
         _check(f"latent_kv_post.{name}", t, torch.int32)
     T, ld = proj.shape
     page_size = c_pages.shape[2]
-    if (tuple(cq.shape) != (T, q_rank) or tuple(gate.shape) != (T, heads) or c_pages.shape[1] != 1 or c_pages.shape[3] != rank
+    if (tuple(cq.shape) != (T, q_rank) or (gate is not None and tuple(gate.shape) != (T, heads)) or c_pages.shape[1] != 1
+            or c_pages.shape[3] != rank
             or tuple(r_pages.shape) != (c_pages.shape[0], 1, page_size, rot) or q_norm.numel() != q_rank
             or kv_norm.numel() != rank or freq.numel() * 2 != dims or kv_col < q_rank or kv_col + rank + rot > ld
-            or gate_col < 0 or gate_col + heads > ld or positions.numel() != T or tok_seq.numel() != T):
+            or (gate is not None and (gate_col < 0 or gate_col + heads > ld)) or positions.numel() != T
+            or tok_seq.numel() != T):
         raise KernelError(f"latent_kv_post: proj {tuple(proj.shape)}, cq {tuple(cq.shape)}, c {tuple(c_pages.shape)}, "
-                          f"r {tuple(r_pages.shape)}, gate {tuple(gate.shape)}")
+                          f"r {tuple(r_pages.shape)}")
     code = library().q3_latent_kv_post(
         proj.data_ptr(), ld, int(q_rank), int(kv_col), int(rank), int(rot), int(dims), int(gate_col), int(heads),
         q_norm.data_ptr(), kv_norm.data_ptr(), float(eps), freq.data_ptr(), float(magnitude), positions.data_ptr(),
         tok_seq.data_ptr(), table.data_ptr(), table.shape[1], page_size, c_pages.shape[0], cq.data_ptr(),
-        c_pages.data_ptr(), r_pages.data_ptr(), gate.data_ptr(), 1 if write_cache else 0, dtype_tag(proj.dtype), T,
-        status.data_ptr(), _stream())
+        c_pages.data_ptr(), r_pages.data_ptr(), _ptr(gate), 1 if write_cache else 0, dtype_tag(proj.dtype), T,
+        rotary_pairing(pairing), status.data_ptr(), _stream())
     _done("latent_kv_post", code, f"ranks {q_rank}/{rank}, rot {rot}")
 
 
 def latent_q_post(q: torch.Tensor, heads: int, dim: int, rot: int, dims: int, freq: torch.Tensor, magnitude: float,
-                  positions: torch.Tensor, q_plain: torch.Tensor, q_rot: torch.Tensor) -> None:
+                  positions: torch.Tensor, q_plain: torch.Tensor, q_rot: torch.Tensor, pairing: str = "halves") -> None:
     """q [T, heads * (dim + rot)] -> q_plain [T, heads * dim] (as it is) and q_rot [T, heads, rot] (rotated by position)."""
     _check("latent_q_post.q", q)
     _check("latent_q_post.q_plain", q_plain, q.dtype)
@@ -1480,16 +1506,17 @@ def latent_q_post(q: torch.Tensor, heads: int, dim: int, rot: int, dims: int, fr
         raise KernelError(f"latent_q_post: q {tuple(q.shape)}, q_plain {tuple(q_plain.shape)}, q_rot {tuple(q_rot.shape)}")
     code = library().q3_latent_q_post(q.data_ptr(), int(heads), int(dim), int(rot), int(dims), freq.data_ptr(),
                                       float(magnitude), positions.data_ptr(), q_plain.data_ptr(), q_rot.data_ptr(),
-                                      dtype_tag(q.dtype), T, _stream())
+                                      dtype_tag(q.dtype), T, rotary_pairing(pairing), _stream())
     _done("latent_q_post", code, f"heads {heads} of {dim}+{rot}")
 
 
 def latent_attn_ref(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor, r_pages: torch.Tensor,
                     positions: torch.Tensor, tok_seq: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float,
-                    status: torch.Tensor) -> None:
+                    status: torch.Tensor, sink: Optional[torch.Tensor] = None) -> None:
     """Causal softmax attention over latents: q_abs float32 [H, T, rank] (the plain query taken through the key
     up-projection), q_rot [T, H, rot]; score = (q_abs . c + q_rot . r) * scale over the keys 0 .. position of the
-    token's request; out [T, H * rank] = sum_j p_j c_j.  A warp per (token, head), keys one by one."""
+    token's request; out [T, H * rank] = sum_j p_j c_j.  A warp per (token, head), keys one by one.  ``sink``: float32
+    [H] or None: exp(sink_h) joins the denominator of head h's softmax (no key, no value, not scaled)."""
     _check("latent_attn_ref.q_abs", q_abs, torch.float32)
     _check("latent_attn_ref.q_rot", q_rot)
     _check("latent_attn_ref.c_pages", c_pages, q_rot.dtype)
@@ -1499,26 +1526,31 @@ def latent_attn_ref(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Ten
         _check(f"latent_attn_ref.{name}", t, torch.int32)
     H, T, rank = q_abs.shape
     rot = q_rot.shape[2]
+    if sink is not None:
+        _check("latent_attn_ref.sink", sink, torch.float32)
     if (tuple(q_rot.shape) != (T, H, rot) or tuple(out.shape) != (T, H * rank) or c_pages.shape[1] != 1
-            or c_pages.shape[3] != rank or r_pages.shape[3] != rot or r_pages.shape[:3] != c_pages.shape[:3]):
+            or c_pages.shape[3] != rank or r_pages.shape[3] != rot or r_pages.shape[:3] != c_pages.shape[:3]
+            or (sink is not None and sink.numel() != H)):
         raise KernelError(f"latent_attn_ref: q_abs {tuple(q_abs.shape)}, q_rot {tuple(q_rot.shape)}, c "
                           f"{tuple(c_pages.shape)}, r {tuple(r_pages.shape)}, out {tuple(out.shape)}")
     code = library().q3_latent_attn_ref(q_abs.data_ptr(), q_rot.data_ptr(), c_pages.data_ptr(), r_pages.data_ptr(),
                                         positions.data_ptr(), tok_seq.data_ptr(), table.data_ptr(), table.shape[1],
                                         c_pages.shape[2], c_pages.shape[0], out.data_ptr(), dtype_tag(out.dtype), T, H,
-                                        rank, rot, float(scale), status.data_ptr(), _stream())
+                                        rank, rot, float(scale), _ptr(sink), status.data_ptr(), _stream())
     _done("latent_attn_ref", code, f"heads {H}, rank {rank}, rot {rot}")
 
 
-def gate_heads(o: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, h * dv + v] = o[h, t, v] * gate[t, h]; o float32 [H, T, dv], gate float32 [T, H]."""
+def gate_heads(o: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t, h * dv + v] = o[h, t, v] * gate[t, h]; o float32 [H, T, dv], gate float32 [T, H] (None: no gates, the
+    heads are only laid side by side in the compute dtype)."""
     _check("gate_heads.o", o, torch.float32)
-    _check("gate_heads.gate", gate, torch.float32)
+    if gate is not None:
+        _check("gate_heads.gate", gate, torch.float32)
     _check("gate_heads.out", out)
     H, T, dv = o.shape
-    if tuple(gate.shape) != (T, H) or tuple(out.shape) != (T, H * dv):
-        raise KernelError(f"gate_heads: o {tuple(o.shape)}, gate {tuple(gate.shape)}, out {tuple(out.shape)}")
-    code = library().q3_gate_heads(o.data_ptr(), gate.data_ptr(), out.data_ptr(), dtype_tag(out.dtype), T, H, dv, _stream())
+    if (gate is not None and tuple(gate.shape) != (T, H)) or tuple(out.shape) != (T, H * dv):
+        raise KernelError(f"gate_heads: o {tuple(o.shape)}, out {tuple(out.shape)}")
+    code = library().q3_gate_heads(o.data_ptr(), _ptr(gate), out.data_ptr(), dtype_tag(out.dtype), T, H, dv, _stream())
     _done("gate_heads", code)
 
 
@@ -1639,7 +1671,7 @@ def latent_decode_splits(num_seqs: int, heads: int, max_kv_len: int) -> int:
 
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Tensor, r_pages: torch.Tensor, ctx,
                      table: torch.Tensor, out: torch.Tensor, scale: float, status: torch.Tensor,
-                     partial: Optional[torch.Tensor] = None, kernel: str = "auto") -> None:
+                     partial: Optional[torch.Tensor] = None, kernel: str = "auto", sink: Optional[torch.Tensor] = None) -> None:
     """Attention over latents for one step's batch (``ctx``: its positions, rows and lengths): see ``latent_attn_ref``
     for the arithmetic.  bfloat16 with a latent that ``latent_attention_fast`` takes runs on the tensor cores (rows of
     (token, head) pairs over shared key tiles; with ``partial`` and a step of single tokens the keys of a request are
@@ -1651,8 +1683,12 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Te
     if kernel == "mma" and not fast:
         raise KernelSizeError(f"latent_attention: the tensor-core kernel does not take rank {rank}, rot {rot}, {q_rot.dtype}")
     if not fast:
-        latent_attn_ref(q_abs, q_rot, c_pages, r_pages, ctx.positions, ctx.tok_seq, table, out, scale, status)
+        latent_attn_ref(q_abs, q_rot, c_pages, r_pages, ctx.positions, ctx.tok_seq, table, out, scale, status, sink=sink)
         return
+    if sink is not None:
+        _check("latent_attention.sink", sink, torch.float32)
+        if sink.numel() != H:
+            raise KernelError(f"latent_attention: {sink.numel()} sinks for {H} heads")
     _check("latent_attention.q_abs", q_abs, torch.float32)
     _check("latent_attention.q_rot", q_rot, torch.bfloat16)
     _check("latent_attention.c_pages", c_pages, torch.bfloat16)
@@ -1671,7 +1707,7 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Te
         q_abs.data_ptr(), q_rot.data_ptr(), c_pages.data_ptr(), r_pages.data_ptr(), ctx.q_start.data_ptr(),
         ctx.kv_len.data_ptr(), table.data_ptr(), table.shape[1], c_pages.shape[2], c_pages.shape[0], out.data_ptr(),
         _ptr(partial) if splits > 1 else None, T, ctx.num_seqs, ctx.max_q_len, H, rank, rot, float(scale), splits,
-        status.data_ptr(), _stream())
+        _ptr(sink), status.data_ptr(), _stream())
     _done("latent_attention (mma)", code, f"heads {H}, rank {rank}, rot {rot}, splits {splits}")
 
 
@@ -1790,23 +1826,27 @@ def _pw_pages(name: str, k_pages, v_pages, pk_pages, pv_pages, dtype):
 
 
 def pw_qkv_post(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, heads: int, kv_heads: int, dim: int, vdim: int,
-                q_norm: torch.Tensor, k_norm: torch.Tensor, eps: float, dims: int, freq: torch.Tensor, magnitude: float,
-                positions: torch.Tensor, tok_seq: torch.Tensor, table: torch.Tensor, q_out: torch.Tensor,
+                q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float, dims: int, freq: torch.Tensor,
+                magnitude: float, positions: torch.Tensor, tok_seq: torch.Tensor, table: torch.Tensor, q_out: torch.Tensor,
                 k_pages: torch.Tensor, v_pages: torch.Tensor, write_cache: bool, status: torch.Tensor) -> None:
     """From one product ``proj`` [T, ld] (q at column ``q_col``, k at ``k_col``, v at ``v_col``): RMS norm of the whole q and of
     the whole k projection (weights ``q_norm`` [heads * dim], ``k_norm`` [kv_heads * dim]), rotation of the first
     ``dims`` values of every head by position * freq (sines and cosines times ``magnitude``), q to ``q_out``
-    [T, heads, dim], k and v into their pages."""
+    [T, heads, dim], k and v into their pages.  Without norm weights (both None) q and k are rotated as projected."""
     _check("pw_qkv_post.proj", proj)
+    if (q_norm is None) != (k_norm is None):
+        raise KernelError("pw_qkv_post: norm weights for both q and k, or for neither")
     _check("pw_qkv_post.q_out", q_out, proj.dtype)
     _check("pw_qkv_post.k_pages", k_pages, proj.dtype)
     _check("pw_qkv_post.v_pages", v_pages, proj.dtype)
     for name, t in (("q_norm", q_norm), ("k_norm", k_norm), ("freq", freq)):
-        _check(f"pw_qkv_post.{name}", t, torch.float32)
+        if t is not None:
+            _check(f"pw_qkv_post.{name}", t, torch.float32)
     for name, t in (("positions", positions), ("tok_seq", tok_seq), ("table", table)):
         _check(f"pw_qkv_post.{name}", t, torch.int32)
     T, ld = proj.shape
-    if (tuple(q_out.shape) != (T, heads, dim) or q_norm.numel() != heads * dim or k_norm.numel() != kv_heads * dim
+    if (tuple(q_out.shape) != (T, heads, dim)
+            or (q_norm is not None and (q_norm.numel() != heads * dim or k_norm.numel() != kv_heads * dim))
             or freq.numel() < dims // 2 or k_col + kv_heads * dim > ld or v_col + kv_heads * vdim > ld
             or q_col < 0 or q_col + heads * dim > ld or k_col < 0 or v_col < 0
             or tuple(k_pages.shape[1:]) != (kv_heads, k_pages.shape[2], dim)
@@ -1814,8 +1854,8 @@ def pw_qkv_post(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, heads: i
         raise KernelError(f"pw_qkv_post: proj {tuple(proj.shape)}, q_out {tuple(q_out.shape)}, k pages "
                           f"{tuple(k_pages.shape)}, v pages {tuple(v_pages.shape)}")
     code = library().q3_pw_qkv_post(proj.data_ptr() + int(q_col) * proj.element_size(), ld, int(k_col) - int(q_col),
-                                    int(v_col) - int(q_col), heads, kv_heads, dim, vdim, q_norm.data_ptr(),
-                                    k_norm.data_ptr(), float(eps), int(dims), freq.data_ptr(), float(magnitude),
+                                    int(v_col) - int(q_col), heads, kv_heads, dim, vdim, _ptr(q_norm),
+                                    _ptr(k_norm), float(eps), int(dims), freq.data_ptr(), float(magnitude),
                                     positions.data_ptr(), tok_seq.data_ptr(), table.data_ptr(), table.shape[1],
                                     k_pages.shape[2], k_pages.shape[0], q_out.data_ptr(), k_pages.data_ptr(),
                                     v_pages.data_ptr(), 1 if write_cache else 0, dtype_tag(proj.dtype), T, status.data_ptr(),
@@ -1843,8 +1883,10 @@ def pool_blocks(k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Te
 def pw_attn_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor,
                 pv_pages: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor, table: torch.Tensor,
                 ptable: torch.Tensor, out: torch.Tensor, window: int, pool: int, scale: float, softcap: Optional[float],
-                out_scale: float, status: torch.Tensor) -> None:
-    """Softmax attention of q [T, H, D] over the last ``window`` tokens and the pooled blocks before them; head h's
+                out_scale: float, status: torch.Tensor, block_limit: int = -1) -> None:
+    """Softmax attention of q [T, H, D] over the last ``window`` tokens and the pooled blocks before them (with
+    ``block_limit`` >= 0 only the first so many blocks are ever read: with blocks of one token whose pages are the
+    token pages themselves, that is a window that also keeps a request's first tokens); head h's
     result times ``out_scale`` goes to columns h * vdim .. of ``out`` (rows of any pitch: a column view of a wider
     buffer is taken).  A warp per (token, head), float32 arithmetic, keys one by one."""
     _check("pw_attn_ref.q", q)
@@ -1862,7 +1904,7 @@ def pw_attn_ref(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, p
                                     table.shape[1], k_pages.shape[0], ptable.data_ptr(), ptable.shape[1], pk_pages.shape[0],
                                     k_pages.shape[2], out.data_ptr(), out.stride(0), dtype_tag(q.dtype), T, H, G, D, Dv,
                                     int(window), int(pool), float(scale), float(softcap or 0.0), float(out_scale),
-                                    status.data_ptr(), _stream())
+                                    int(block_limit), status.data_ptr(), _stream())
     _done("pw_attn_ref", code, f"heads {H}/{G}, dim {D}, vdim {Dv}")
 
 
@@ -1874,7 +1916,7 @@ def pw_attention_fast(dtype: torch.dtype, dim: int, vdim: int) -> bool:
 def pw_attn_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor,
                 pv_pages: torch.Tensor, ctx, table: torch.Tensor, ptable: torch.Tensor, out: torch.Tensor, window: int,
                 pool: int, scale: float, softcap: Optional[float], out_scale: float, status: torch.Tensor,
-                partial: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
+                partial: Optional[Tuple[torch.Tensor, torch.Tensor]] = None, block_limit: int = -1) -> None:
     """The same attention as ``pw_attn_ref`` on the tensor cores (bfloat16): tiles of 64 entries of the block pages
     and of the token pages in one online softmax, 128 (token, head) rows of one kv head to a block.  ``partial``
     (``pw_attn_partial``): scratch with which a step of single tokens cuts every request's keys into ranges that run
@@ -1901,8 +1943,8 @@ def pw_attn_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, p
                                     ctx.kv_len.data_ptr(), table.data_ptr(), table.shape[1], k_pages.shape[0],
                                     ptable.data_ptr(), ptable.shape[1], pk_pages.shape[0], k_pages.shape[2], ctx.num_seqs,
                                     ctx.max_q_len, H, G, D, Dv, float(scale), float(softcap or 0.0), float(out_scale),
-                                    int(window), int(pool), T, _ptr(part_o), _ptr(part_ml), part_rows, status.data_ptr(),
-                                    _stream())
+                                    int(window), int(pool), int(block_limit), T, _ptr(part_o), _ptr(part_ml), part_rows,
+                                    status.data_ptr(), _stream())
     _done("pw_attn_mma", code, f"heads {H}/{G}, dim {D}, vdim {Dv}")
 
 
@@ -1920,16 +1962,17 @@ def pw_attn_partial(alloc, max_seqs: int, heads: int, vdim: int) -> Tuple[torch.
 def pooled_window_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, pk_pages: torch.Tensor,
                             pv_pages: torch.Tensor, ctx, table: torch.Tensor, ptable: torch.Tensor, out: torch.Tensor,
                             window: int, pool: int, scale: float, softcap: Optional[float], out_scale: float,
-                            status: torch.Tensor, partial: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
+                            status: torch.Tensor, partial: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
+                            block_limit: int = -1) -> None:
     """The attention of a step's batch over windows and pooled blocks, by the kernel that suits dtype and shape: the
     tensor-core kernel for bfloat16 heads it takes (an output whose rows and start allow paired stores), the plain
     one for everything else."""
     if (pw_attention_fast(q.dtype, q.shape[2], v_pages.shape[3]) and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
         pw_attn_mma(q, k_pages, v_pages, pk_pages, pv_pages, ctx, table, ptable, out, window, pool, scale, softcap,
-                    out_scale, status, partial)
+                    out_scale, status, partial, block_limit)
     else:
         pw_attn_ref(q, k_pages, v_pages, pk_pages, pv_pages, ctx.positions, ctx.tok_seq, table, ptable, out, window, pool,
-                    scale, softcap, out_scale, status)
+                    scale, softcap, out_scale, status, block_limit)
 
 
 # ------------------------------------------------------------------ a recurrence gated by the current token alone
@@ -2015,27 +2058,33 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor
 
 
 def moe_pairs(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-              base: Optional[torch.Tensor], act_buf: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+              base: Optional[torch.Tensor], act_buf: torch.Tensor, out: torch.Tensor, activation: str,
+              gate_block: int = 0, in_weights: Optional[torch.Tensor] = None) -> None:
     """out[t] = base[t] + sum_k weights[t, k] down[ids[t, k]] act(up[ids[t, k]] h[t]); up [E, F, W], down [E, W, F];
-    ``act_buf`` [T * top, F] receives the activations.  Every (token, expert) pair streams its expert once."""
+    ``act_buf`` [T * top, F] receives the activations.  Every (token, expert) pair streams its expert once.
+    ``gate_block`` > 0: gated experts, act(gate h) * (up h), ``up`` being [E, 2 F, W] with gate and up rows alternating
+    in blocks of so many rows.  ``in_weights`` [T, top]: what multiplies the expert's input (``weights`` still
+    multiply its output: ones, for a design that weighs the input only)."""
     _check("moe_pairs.h", h)
     for name, t in (("up", up), ("down", down), ("act_buf", act_buf), ("out", out)):
         _check(f"moe_pairs.{name}", t, h.dtype)
     _check("moe_pairs.ids", ids, torch.int32)
     _check("moe_pairs.weights", weights, torch.float32)
     T, W = h.shape
-    E, F = up.shape[0], up.shape[1]
+    E, F = up.shape[0], up.shape[1] // (2 if gate_block else 1)
     top = ids.shape[1]
     if base is not None:
         _check("moe_pairs.base", base, h.dtype)
-    if (tuple(up.shape) != (E, F, W) or tuple(down.shape) != (E, W, F) or tuple(ids.shape) != (T, top)
+    if in_weights is not None:
+        _check("moe_pairs.in_weights", in_weights, torch.float32)
+    if (tuple(up.shape) != (E, F * (2 if gate_block else 1), W) or (in_weights is not None and in_weights.shape != weights.shape) or tuple(down.shape) != (E, W, F) or tuple(ids.shape) != (T, top)
             or tuple(weights.shape) != (T, top) or tuple(act_buf.shape) != (T * top, F) or tuple(out.shape) != (T, W)
             or (base is not None and tuple(base.shape) != (T, W))):
         raise KernelError(f"moe_pairs: h {tuple(h.shape)}, up {tuple(up.shape)}, down {tuple(down.shape)}, ids "
                           f"{tuple(ids.shape)}, activations {tuple(act_buf.shape)}, out {tuple(out.shape)}")
     code = library().q3_moe_pairs(h.data_ptr(), up.data_ptr(), down.data_ptr(), ids.data_ptr(), weights.data_ptr(),
                                   _ptr(base), act_buf.data_ptr(), out.data_ptr(), dtype_tag(h.dtype), T, W, F, E, top,
-                                  activation_code(activation, gate=True), _stream())
+                                  activation_code(activation, gate=True), int(gate_block), _ptr(in_weights), _stream())
     _done("moe_pairs", code, f"experts {E}, top {top}, inner {F}")
 
 
@@ -2054,9 +2103,20 @@ def moe_grouped_tiles(num_tokens: int, top: int, experts: int) -> int:
     return (num_tokens * top) // moe_tile_rows() + experts
 
 
-def moe_grouped_takes(dtype: torch.dtype, width: int, ff: int) -> bool:
-    """Whether the grouped products take these experts: bfloat16, rows of whole 16-byte pieces."""
-    return dtype == torch.bfloat16 and width % 8 == 0 and ff % 8 == 0
+MOE_GATE_BLOCK = 16  # rows of a gated expert's stack alternate between gate and up in blocks of so many
+
+
+def moe_gate_block(ff: int) -> int:
+    """How the rows of a gated expert's two first matrices are interleaved: in blocks of ``MOE_GATE_BLOCK`` where the
+    inner width is a multiple of it (the grouped product's epilogue then finds a gate and its up value in one piece),
+    else all gate rows and then all up rows."""
+    return MOE_GATE_BLOCK if ff % MOE_GATE_BLOCK == 0 else ff
+
+
+def moe_grouped_takes(dtype: torch.dtype, width: int, ff: int, gated: bool = False) -> bool:
+    """Whether the grouped products take these experts: bfloat16, rows of whole 16-byte pieces (gated experts: an
+    inner width in multiples of ``MOE_GATE_BLOCK``)."""
+    return dtype == torch.bfloat16 and width % 8 == 0 and ff % (MOE_GATE_BLOCK if gated else 8) == 0
 
 
 class MoeScratch:
@@ -2075,7 +2135,7 @@ class MoeScratch:
 
 def moe_grouped(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
                 base: Optional[torch.Tensor], out: torch.Tensor, activation: str, scratch: MoeScratch,
-                status: torch.Tensor) -> None:
+                status: torch.Tensor, gated: bool = False, in_weights: Optional[torch.Tensor] = None) -> None:
     """out = base + sum_k weights[:, k] * down[ids[:, k]] act(up[ids[:, k]] h) for many tokens (bfloat16): the pairs
     sorted by expert into whole tiles, both products of all experts as one grouped tensor-core product each."""
     _check("moe_grouped.h", h, torch.bfloat16)
@@ -2085,13 +2145,16 @@ def moe_grouped(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torc
     _check("moe_grouped.weights", weights, torch.float32)
     _check("moe_grouped.out", out, torch.bfloat16)
     T, W = h.shape
-    E, F = up.shape[0], up.shape[1]
+    E, F = up.shape[0], up.shape[1] // (2 if gated else 1)
     top = ids.shape[1]
+    if in_weights is not None:
+        _check("moe_grouped.in_weights", in_weights, torch.float32)
     tiles = moe_grouped_tiles(T, top, E)
     rows = tiles * moe_tile_rows()
     if base is not None:
         _check("moe_grouped.base", base, torch.bfloat16)
-    if (tuple(up.shape) != (E, F, W) or tuple(down.shape) != (E, W, F) or tuple(ids.shape) != (T, top)
+    if (tuple(up.shape) != (E, F * (2 if gated else 1), W) or tuple(down.shape) != (E, W, F) or tuple(ids.shape) != (T, top)
+            or (in_weights is not None and in_weights.shape != weights.shape)
             or tuple(weights.shape) != (T, top) or tuple(out.shape) != (T, W) or (base is not None and base.shape != h.shape)
             or scratch.sorted_in.shape[0] < rows or scratch.sorted_in.shape[1] != W or scratch.sorted_act.shape[1] != F
             or scratch.sorted_out.shape[1] != W or scratch.pos.numel() < T * top):
@@ -2103,16 +2166,155 @@ def moe_grouped(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torc
                                     _ptr(base), out.data_ptr(), scratch.sorted_in.data_ptr(), scratch.sorted_act.data_ptr(),
                                     scratch.sorted_out.data_ptr(), scratch.pos.data_ptr(), scratch.src.data_ptr(),
                                     scratch.meta.data_ptr(), T, W, F, E, top, cap, activation_code(activation, gate=True),
-                                    status.data_ptr(), _stream())
+                                    1 if gated else 0, _ptr(in_weights), status.data_ptr(), _stream())
     _done("moe_grouped", code, f"experts {E}, top {top}, width {W}, ff {F}")
 
 
 def routed_experts(h: torch.Tensor, up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
                    base: Optional[torch.Tensor], act_buf: torch.Tensor, out: torch.Tensor, activation: str,
-                   scratch: Optional[MoeScratch] = None, status: Optional[torch.Tensor] = None) -> None:
+                   scratch: Optional[MoeScratch] = None, status: Optional[torch.Tensor] = None, gate_block: int = 0,
+                   in_weights: Optional[torch.Tensor] = None) -> None:
     """The chosen experts of a step's tokens, by the kernels that suit dtype and shape: with ``scratch``, from
     ``MOE_GROUPED_FROM`` tokens on, the grouped tensor-core products; otherwise a pair at a time (``moe_pairs``)."""
     if scratch is not None and status is not None and h.shape[0] >= MOE_GROUPED_FROM:
-        moe_grouped(h, up, down, ids, weights, base, out, activation, scratch, status)
+        moe_grouped(h, up, down, ids, weights, base, out, activation, scratch, status, gated=gate_block > 0,
+                    in_weights=in_weights)
     else:
-        moe_pairs(h, up, down, ids, weights, base, act_buf, out, activation)
+        moe_pairs(h, up, down, ids, weights, base, act_buf, out, activation, gate_block, in_weights)
+
+
+# ------------------------------------------------------------------ Dynamic Tanh around sub-layers, a token's second embedding
+def add_dyt(stream: torch.Tensor, delta: Optional[torch.Tensor], after, before, out: Optional[torch.Tensor],
+            rows_add: Optional[torch.Tensor] = None, vec_add: Optional[torch.Tensor] = None,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """stream += after(delta) + rows_add + vec_add (each optional), then out = before(stream).  ``after`` and ``before``
+    are (alpha, weight, bias) of a Dynamic Tanh, tanh(alpha x) w + b, alpha a float32 tensor of one value on the
+    device, or None for the identity.  ``out``: [T, W] in the compute dtype or float32, or None.  ``rows`` (int32):
+    only these rows are worked out, into ``out`` [len(rows), W], and the stream stays as it is."""
+    _check("add_dyt.stream", stream, torch.float32)
+    T, W = stream.shape
+    dtype = delta.dtype if delta is not None else (out.dtype if out is not None else torch.float32)
+    if delta is not None:
+        _check("add_dyt.delta", delta)
+    if out is not None:
+        _check("add_dyt.out", out)
+        if out.dtype != dtype and out.dtype != torch.float32:
+            raise KernelError(f"add_dyt: out is {out.dtype}, the step's dtype is {dtype}")
+    for name, t in (("rows_add", rows_add), ("vec_add", vec_add)):
+        if t is not None:
+            _check(f"add_dyt.{name}", t, torch.float32)
+    args = []
+    for name, norm in (("after", after), ("before", before)):
+        if norm is None:
+            args += [None, None, None]
+            continue
+        alpha, weight, bias = norm
+        for t in (alpha, weight, bias):
+            _check(f"add_dyt.{name}", t, torch.float32)
+        if alpha.numel() != 1 or weight.numel() != W or bias.numel() != W:
+            raise KernelError(f"add_dyt: {name} has alpha {tuple(alpha.shape)}, weight {tuple(weight.shape)} for width {W}")
+        args += [alpha.data_ptr(), weight.data_ptr(), bias.data_ptr()]
+    R = 0
+    if rows is not None:
+        _check("add_dyt.rows", rows, torch.int32)
+        R = rows.numel()
+    n = R if rows is not None else T
+    if ((delta is not None and tuple(delta.shape) != (T, W)) or (out is not None and tuple(out.shape) != (n, W))
+            or (rows_add is not None and tuple(rows_add.shape) != (T, W)) or (vec_add is not None and vec_add.numel() != W)
+            or (rows is not None and out is None)):
+        raise KernelError(f"add_dyt: stream {tuple(stream.shape)}, delta {None if delta is None else tuple(delta.shape)}, "
+                          f"out {None if out is None else tuple(out.shape)}")
+    out_f32 = out is not None and out.dtype == torch.float32 and dtype != torch.float32
+    code = library().q3_add_dyt(stream.data_ptr(), _ptr(delta), args[0], args[1], args[2], _ptr(rows_add), _ptr(vec_add),
+                                args[3], args[4], args[5], _ptr(out), 1 if out_f32 else 0, _ptr(rows), R, dtype_tag(dtype),
+                                T, W, _stream())
+    _done("add_dyt", code, f"rows {n}, width {W}")
+
+
+def side_gate(p: torch.Tensor, side: torch.Tensor, column: int, out: torch.Tensor) -> None:
+    """out = gelu_tanh(p) * side[:, column : column + dim]; p, out [T, dim] in the compute dtype, side float32 [T, any]."""
+    _check("side_gate.p", p)
+    _check("side_gate.out", out, p.dtype)
+    _check("side_gate.side", side, torch.float32)
+    T, dim = p.shape
+    if tuple(out.shape) != (T, dim) or side.shape[0] != T or column < 0 or column + dim > side.shape[1]:
+        raise KernelError(f"side_gate: p {tuple(p.shape)}, side {tuple(side.shape)}, column {column}")
+    code = library().q3_side_gate(p.data_ptr(), side.data_ptr(), side.shape[1], int(column), out.data_ptr(),
+                                  dtype_tag(p.dtype), T, dim, _stream())
+    _done("side_gate", code)
+
+
+def add_unit_rms(stream: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """stream += y / sqrt(mean(y^2) + eps) * weight, row by row; stream float32 [T, W], y [T, W] in the compute dtype."""
+    _check("add_unit_rms.stream", stream, torch.float32)
+    _check("add_unit_rms.y", y)
+    _check("add_unit_rms.weight", weight, torch.float32)
+    T, W = stream.shape
+    if tuple(y.shape) != (T, W) or weight.numel() != W:
+        raise KernelError(f"add_unit_rms: stream {tuple(stream.shape)}, y {tuple(y.shape)}, weight {tuple(weight.shape)}")
+    code = library().q3_add_unit_rms(stream.data_ptr(), y.data_ptr(), weight.data_ptr(), float(eps), dtype_tag(y.dtype), T,
+                                     W, _stream())
+    _done("add_unit_rms", code)
+
+
+def sigmoid_gate(x: torch.Tensor, proj: torch.Tensor, column: int) -> None:
+    """x *= sigmoid(proj[:, column : column + n]) in place, n = x.shape[1]; x may be a column view of a wider buffer."""
+    if (x.dim() != 2 or x.stride(1) != 1 or not x.is_cuda or proj.dtype != x.dtype or proj.shape[0] != x.shape[0]
+            or column < 0 or column + x.shape[1] > proj.shape[1]):
+        raise KernelError(f"sigmoid_gate: x {tuple(x.shape)} strides {x.stride()}, proj {tuple(proj.shape)}, column {column}")
+    _check("sigmoid_gate.proj", proj)
+    code = library().q3_sigmoid_gate(x.data_ptr(), x.stride(0), proj.data_ptr(), proj.shape[1], int(column), x.shape[1],
+                                     dtype_tag(x.dtype), x.shape[0], _stream())
+    _done("sigmoid_gate", code)
+
+
+# ------------------------------------------------------------------ the matrix memory of the xLSTM
+def mlstm_max_dim() -> int:
+    """The largest key size per head that ``mlstm_scan`` takes."""
+    if "mlstm max dim" not in _DEVICE_FACTS:
+        _DEVICE_FACTS["mlstm max dim"] = int(library()._lib.q3_mlstm_max_dim())
+    return _DEVICE_FACTS["mlstm max dim"]
+
+
+def mlstm_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, i_col: int, f_col: int, i_bias: torch.Tensor,
+               f_bias: torch.Tensor, cap: float, memory: torch.Tensor, normaliser: torch.Tensor, maximum: torch.Tensor,
+               q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor, status: torch.Tensor) -> None:
+    """The mLSTM recurrence over every request's tokens in order.  ``proj`` [T, any]: q and k (heads * dim each), v
+    (heads * vdim) and the two gates' pre-activations (heads each) from the given columns; state per slot: ``memory``
+    [slots, heads, dim, vdim], ``normaliser`` [slots, heads, dim], ``maximum`` [slots, heads], float32, read and
+    renewed; ``out`` float32 [T, heads * vdim]: S^T q / (max(|n . q|, exp(-m)) + 1e-6) with q times dim^-1/2."""
+    _check("mlstm_scan.proj", proj)
+    for name, t in (("i_bias", i_bias), ("f_bias", f_bias), ("memory", memory), ("normaliser", normaliser),
+                    ("maximum", maximum), ("out", out)):
+        _check(f"mlstm_scan.{name}", t, torch.float32)
+    for name, t in (("q_start", q_start), ("slot_ids", slot_ids)):
+        _check(f"mlstm_scan.{name}", t, torch.int32)
+    T, ld = proj.shape
+    slots, H, D, Dv = memory.shape
+    if (tuple(normaliser.shape) != (slots, H, D) or tuple(maximum.shape) != (slots, H) or tuple(out.shape) != (T, H * Dv)
+            or i_bias.numel() != H or f_bias.numel() != H or min(q_col, k_col, v_col, i_col, f_col) < 0
+            or max(q_col + H * D, k_col + H * D, v_col + H * Dv, i_col + H, f_col + H) > ld):
+        raise KernelError(f"mlstm_scan: proj {tuple(proj.shape)}, memory {tuple(memory.shape)}, out {tuple(out.shape)}")
+    code = library().q3_mlstm_scan(proj.data_ptr(), ld, int(q_col), int(k_col), int(v_col), int(i_col), int(f_col),
+                                   i_bias.data_ptr(), f_bias.data_ptr(), float(cap), memory.data_ptr(),
+                                   normaliser.data_ptr(), maximum.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(),
+                                   slots, out.data_ptr(), dtype_tag(proj.dtype), int(num_seqs), H, D, Dv,
+                                   status.data_ptr(), _stream())
+    _done("mlstm_scan", code, f"heads {H}, dim {D}, vdim {Dv}")
+
+
+def mlstm_out(o: torch.Tensor, proj: torch.Tensor, g_col: int, weight: torch.Tensor, eps: float, out: torch.Tensor,
+              out_scale: float, heads: int) -> None:
+    """out = o / rms_per_head(o) * weight * sigmoid(proj[:, g_col:]) * out_scale; o float32 [T, heads * vdim]; ``out`` in
+    the compute dtype, possibly a column view of a wider buffer."""
+    _check("mlstm_out.o", o, torch.float32)
+    _check("mlstm_out.proj", proj)
+    _check("mlstm_out.weight", weight, torch.float32)
+    T, n = o.shape
+    if (n % heads or out.dtype != proj.dtype or out.dim() != 2 or tuple(out.shape) != (T, n) or out.stride(1) != 1
+            or weight.numel() != n or g_col < 0 or g_col + n > proj.shape[1] or proj.shape[0] != T):
+        raise KernelError(f"mlstm_out: o {tuple(o.shape)}, proj {tuple(proj.shape)}, out {tuple(out.shape)}")
+    code = library().q3_mlstm_out(o.data_ptr(), proj.data_ptr(), proj.shape[1], int(g_col), weight.data_ptr(), float(eps),
+                                  float(out_scale), out.data_ptr(), out.stride(0), dtype_tag(proj.dtype), T, int(heads),
+                                  n // heads, _stream())
+    _done("mlstm_out", code)

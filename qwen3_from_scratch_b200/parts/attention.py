@@ -1,6 +1,8 @@
 """Attention mixers over a paged cache: grouped-query softmax attention (with optional per-head RMSNorm of q and
-k, an optional position encoding and an optional sliding window), sigmoid attention whose values are its keys, and
-softmax attention through a latent (one latent vector and one rotated key part per token, shared by the heads).
+k, an optional position encoding and an optional sliding window), sigmoid attention whose values are its keys,
+softmax attention through a latent (one latent vector and one rotated key part per token, shared by the heads; with
+optional output gates and an optional sink in the softmax), softmax attention over a window and pooled blocks, and
+softmax attention over a window that also keeps a request's first tokens.
 
 Reference: models/self_attn.py:300-386 (packed [T, hidden] input, merged QKV, head norm then
 rotation, keys/values written to pages, causal attention over the cache, output projection),
@@ -239,6 +241,11 @@ class LatentAttention(Mixer):
         score(head) = (q_plain . W_uk,head c + q_rot . r) * scale;   value(head) = W_uv,head c
         out = W_o concat_heads(sigmoid(W_g h)_head * softmax(scores) values)
 
+    ``gate=False``: no W_g, the heads' outputs go to W_o as they are.  ``sink=True``: a learned number per head
+    (``<name>.sink``) whose exponential joins the softmax's denominator: it has no key and no value and is not scaled.
+    ``pairing``: which values of a rotated part turn together, "halves" (i with i + dims / 2) or "neighbours" (2i with
+    2i + 1); the frequencies are the position part's either way.
+
     Per token the cache holds only c (plane ``c``) and r (plane ``r``), one "head" each.  Keys and values are never
     formed: the plain query is taken through W_uk once (q' = W_uk,head^T q_plain, ``kv_rank`` values), the kernels
     attend over the latents themselves, and the result goes through W_uv,head afterwards.  ``scale`` is used as given.
@@ -247,11 +254,14 @@ class LatentAttention(Mixer):
 
     graph_capturable = True
     NAMES = {"dq": "dq", "dq_norm": "dq.norm", "uq": "uq", "dkv": "dkv", "dkv_norm": "dkv.norm", "uk": "uk", "uv": "uv",
-             "gate": "g", "out": "o"}
+             "gate": "g", "out": "o", "sink": "sink"}
 
     def __init__(self, name: str, hidden_size: int, num_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
-                 q_rank: int, scale: float, norm_eps: float, position: PartSpec, names: Optional[Dict[str, str]] = None):
+                 q_rank: int, scale: float, norm_eps: float, position: PartSpec, names: Optional[Dict[str, str]] = None,
+                 gate: bool = True, sink: bool = False, pairing: str = "halves"):
         super().__init__(name)
+        self.has_gate, self.has_sink, self.pairing = bool(gate), bool(sink), str(pairing)
+        ops.rotary_pairing(self.pairing)
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
         self.dim, self.rot_dim, self.vdim = int(dim), int(rot_dim), int(vdim)
         self.kv_rank, self.q_rank = int(kv_rank), int(q_rank)
@@ -269,8 +279,9 @@ class LatentAttention(Mixer):
                 WeightSpec(t["dkv"], (self.kv_rank + self.rot_dim, w)),
                 WeightSpec(t["dkv_norm"], (self.kv_rank,), kind="vector", init="one_plus_normal"),
                 WeightSpec(t["uk"], (H * self.dim, self.kv_rank)),
-                WeightSpec(t["uv"], (H * self.vdim, self.kv_rank)),
-                WeightSpec(t["gate"], (H, w)),
+                WeightSpec(t["uv"], (H * self.vdim, self.kv_rank))] + (
+                    [WeightSpec(t["gate"], (H, w))] if self.has_gate else []) + (
+                    [WeightSpec(t["sink"], (H,), kind="vector", init="normal")] if self.has_sink else []) + [
                 WeightSpec(t["out"], (w, H * self.vdim))] + self.position.weight_specs()
 
     def cache_spec(self) -> PagedCacheSpec:
@@ -279,11 +290,13 @@ class LatentAttention(Mixer):
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
         t, H = self.tensors, self.num_heads
-        dq, dkv, g = weights.pop(t["dq"]), weights.pop(t["dkv"]), weights.pop(t["gate"])
+        dq, dkv = weights.pop(t["dq"]), weights.pop(t["dkv"])
+        g = weights.pop(t["gate"]) if self.has_gate else dq[:0]
+        self.sink = weights[t["sink"]] if self.has_sink else None
         dtype = torch.float32 if torch.float32 in (dq.dtype, dkv.dtype, g.dtype) else dq.dtype
         # one product reads the input: query latent, kv latent with the shared key part, gates (padded to whole
         # groups of eight rows so that the few-rows product takes it)
-        rows = self.q_rank + self.kv_rank + self.rot_dim + H
+        rows = self.q_rank + self.kv_rank + self.rot_dim + g.shape[0]
         pad = torch.zeros((-rows) % 8, dq.shape[1], dtype=dtype, device=dq.device)
         self.down = Linear(torch.cat([dq.to(dtype), dkv.to(dtype), g.to(dtype), pad], dim=0), rt, tag="lattn.down")
         del dq, dkv, g
@@ -300,7 +313,7 @@ class LatentAttention(Mixer):
         self.position.setup(rt, weights)
         T = rt.max_tokens
         self._cq = rt.shared("lattn.cq", T, self.q_rank)
-        self._gate = rt.shared("lattn.gate", T, H, dtype=torch.float32)
+        self._gate = rt.shared("lattn.gate", T, H, dtype=torch.float32) if self.has_gate else None
         self._q_plain = rt.shared("lattn.q_plain", T, H * self.dim)
         self._q_rot = rt.shared("lattn.q_rot", T, H, self.rot_dim)
         self._q_abs = rt.shared("lattn.q_abs", H * T * self.kv_rank, dtype=torch.float32)
@@ -318,16 +331,18 @@ class LatentAttention(Mixer):
         c_pages, r_pages = planes["c"], planes["r"]
         freq, mag, dims = self.position.frequencies()
         status = self.rt.status
-        cq, gate = self._cq[:T], self._gate[:T]
+        cq, gate = self._cq[:T], (self._gate[:T] if self.has_gate else None)
         ops.latent_kv_post(self.down(x), self.q_rank, self.kv_col, rank, rot, dims, self.gate_col, H, self.q_norm,
                            self.kv_norm, self.norm_eps, freq, mag, ctx.positions, ctx.tok_seq, table, c_pages, r_pages, cq,
-                           gate, write_cache, status)
+                           gate, write_cache, status, pairing=self.pairing)
         q_plain, q_rot = self._q_plain[:T], self._q_rot[:T]
-        ops.latent_q_post(self.up_q(cq), H, self.dim, rot, dims, freq, mag, ctx.positions, q_plain, q_rot)
+        ops.latent_q_post(self.up_q(cq), H, self.dim, rot, dims, freq, mag, ctx.positions, q_plain, q_rot,
+                          pairing=self.pairing)
         q_abs = self._q_abs[: H * T * rank].view(H, T, rank)
         ops.block_diag(q_plain, self.uk_t, q_abs)
         o_lat = self._o_lat[:T]
-        ops.latent_attention(q_abs, q_rot, c_pages, r_pages, ctx, table, o_lat, self.scale, status, partial=self._partial)
+        ops.latent_attention(q_abs, q_rot, c_pages, r_pages, ctx, table, o_lat, self.scale, status, partial=self._partial,
+                             sink=self.sink)
         o_heads = self._o_heads[: H * T * self.vdim].view(H, T, self.vdim)
         ops.block_diag(o_lat, self.uv, o_heads)
         out = self._o[:T]
@@ -440,6 +455,106 @@ class PooledWindowAttention(Mixer):
                             ctx.num_seqs, ctx.max_q_len, self.pool, status)
         ops.pooled_window_attention(q, planes["k"], planes["v"], pooled["pk"], pooled["pv"], ctx, table, ptable, out,
                                     self.window, self.pool, self.scale, self.softcap, out_scale, status, self._partial)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        o = self._o[: x.shape[0]]
+        self.core(self.in_proj(x), 0, ctx, cache_id, write_cache, o, 1.0)
+        return self.out_proj(o)
+
+
+@register_part("mixer", "kept_window_attention")
+class KeptWindowAttention(Mixer):
+    """Grouped-query softmax attention over a sliding window that also keeps a request's first tokens.  With h the
+    input, H heads on G key/value heads (head n reads key/value head n // (H / G)), keys of ``dim`` and values of
+    ``vdim`` values:
+
+        q = W_q h;  k = W_k h;  v = W_v h;  q, k rotated by ``position`` (a part with ``frequencies()``: the first ``dims``
+        values of every head, value i with value i + dims / 2), the values not
+        score = q . k * scale;  position i reads j <= i with i - j < window or j < keep_first, the kept tokens at their
+        true positions;  ordinary softmax over what is read
+        out = W_o (concat_heads(softmax(scores) values) * sigmoid(W_g h))          (``gate``; without it no W_g)
+
+    One paged cache (planes ``k`` and ``v``), of which the manager keeps the pages of the last ``window`` tokens and those
+    of the first ``keep_first``.  The attention kernels are those of the window with pooled blocks, run with blocks of
+    one token whose pages are the token pages themselves and with no more than ``keep_first`` of them.  ``scale`` is used
+    as given.  Angles, scores, weights and the gate are float32 in every run.  ``names``: the tensors' names after the
+    part's own."""
+
+    graph_capturable = True
+    splittable = True
+    NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o"}
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
+                 window: int, keep_first: int, position: PartSpec, gate: bool = True, names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"{self.num_heads} query heads are not a multiple of {self.num_kv_heads} kv heads")
+        self.dim, self.vdim, self.scale = int(dim), int(vdim), float(scale)
+        self.window, self.keep_first, self.has_gate = int(window), int(keep_first), bool(gate)
+        if self.window < 1 or self.keep_first < 0:
+            raise ValueError(f"attention {name}: window {self.window} must be positive, keep_first {self.keep_first} not negative")
+        self.position = create_part("position", position, name=f"{name}.position")
+        n = dict(self.NAMES)
+        n.update(names or {})
+        self.tensors = {k: f"{name}.{v}" for k, v in n.items()}
+
+    def weight_specs(self) -> List[WeightSpec]:
+        t, w, H, G, D, Dv = self.tensors, self.hidden_size, self.num_heads, self.num_kv_heads, self.dim, self.vdim
+        return [WeightSpec(t["q"], (H * D, w)), WeightSpec(t["k"], (G * D, w)), WeightSpec(t["v"], (G * Dv, w))] + (
+            [WeightSpec(t["gate"], (H * Dv, w))] if self.has_gate else []) + [
+            WeightSpec(t["out"], (w, H * Dv))] + self.position.weight_specs()
+
+    def cache_spec(self):
+        G = self.num_kv_heads
+        return PagedCacheSpec((CachePlane("k", G, self.dim), CachePlane("v", G, self.vdim)), window=self.window,
+                              keep_first=self.keep_first)
+
+    # ------------------------------------------------------------------ the two products and what lies between
+    def input_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        t = self.tensors
+        parts = [weights.pop(t[k]) for k in (("q", "k", "v", "gate") if self.has_gate else ("q", "k", "v"))]
+        dtype = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
+        return torch.cat([p.to(dtype) for p in parts], dim=0)  # columns of the product: q, k, v, gates
+
+    def output_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        return weights.pop(self.tensors["out"])
+
+    @property
+    def output_columns(self) -> int:
+        return self.num_heads * self.vdim
+
+    def setup_core(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        self.rt = rt
+        self.position.setup(rt, weights)
+        self._q = rt.shared("kwattn.q", rt.max_tokens, self.num_heads, self.dim)
+        self._partial = None
+        if ops.pw_attention_fast(rt.dtype, self.dim, self.vdim):
+            self._partial = ops.pw_attn_partial(rt.shared, rt.max_seqs, self.num_heads, self.vdim)
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        self.in_proj = Linear(self.input_weight(weights), rt, tag="kwattn.in")
+        self.out_proj = Linear(self.output_weight(weights), rt, tag="kwattn.out")
+        self.setup_core(rt, weights)
+        self._o = rt.shared("kwattn.o", rt.max_tokens, self.output_columns)
+
+    def core(self, proj: torch.Tensor, column: int, ctx: StepContext, cache_id: Optional[int], write_cache: bool,
+             out: torch.Tensor, out_scale: float) -> None:
+        T, H, G, D, Dv = proj.shape[0], self.num_heads, self.num_kv_heads, self.dim, self.vdim
+        planes, table = ctx.pages(cache_id)
+        k_pages, v_pages = planes["k"], planes["v"]
+        freq, mag, dims = self.position.frequencies()
+        status = self.rt.status
+        q = self._q[:T]
+        k_col, v_col = column + H * D, column + (H + G) * D
+        ops.pw_qkv_post(proj, column, k_col, v_col, H, G, D, Dv, None, None, 0.0, dims, freq, mag, ctx.positions,
+                        ctx.tok_seq, table, q, k_pages, v_pages, write_cache, status)
+        # the kept first tokens are "blocks" of one token read from the token pages, at most keep_first of them
+        ops.pooled_window_attention(q, k_pages, v_pages, k_pages, v_pages, ctx, table, table, out, self.window, 1,
+                                    self.scale, None, out_scale, status, self._partial, block_limit=self.keep_first)
+        if self.has_gate:
+            ops.sigmoid_gate(out, proj, v_col + G * Dv)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         o = self._o[: x.shape[0]]

@@ -82,13 +82,15 @@ class PagedCacheSpec:
     latent vector per token; keys and values of different widths; ...).  A plane's pages are one tensor
     ``[num_pages, heads, page_size, width]``; all planes of a cache share the page ids.
     ``window`` = how many of the latest tokens a query still reads (None: all of them); pages a window
-    has passed are given back.  ``entry_tokens`` = how many tokens share one slot: with n > 1 the cache holds one
+    has passed are given back, except those that hold any of a request's first ``keep_first`` tokens, which stay as
+    long as the request lives (a window that also reads the first tokens).  ``entry_tokens`` = how many tokens share one slot: with n > 1 the cache holds one
     entry per whole group of n tokens (entry e belongs to the tokens e n .. e n + n - 1 and exists once the last of
     them has been computed), for parts that keep a summary per block of tokens; such a cache has no window."""
 
     planes: Tuple[CachePlane, ...]
     window: Optional[int] = None
     entry_tokens: int = 1
+    keep_first: int = 0
 
     def bytes_per_token(self, compute_itemsize: int) -> int:
         return sum(p.heads * p.width * (4 if p.dtype == "float32" else compute_itemsize) for p in self.planes)
@@ -206,6 +208,8 @@ class StepContext:
 
 
 EMBEDDING_OUTPUT = "embedding.output"  # key in StepContext.per_step: a copy of what the embedding wrote (float32)
+EMBEDDING_SIDE = "embedding.side"  # key in StepContext.per_step: the tokens' rows of the embedding's second table (float32)
+LAYER_REPEAT = "layer.repeat"  # key in StepContext.per_step: which run of its layer the block is in (LayerCall.repeat)
 STREAM_SUMSQ = "stream.sumsq"  # key in StepContext.per_step: StreamStats of the stream as it stands
 NEXT_NORM_WEIGHT = "stream.next_norm_weight"  # key in StepContext.per_step: weight of the next block's first norm
 
@@ -242,6 +246,15 @@ class StreamNorm:
     @property
     def dtype(self):
         return torch.bfloat16
+
+
+@dataclass
+class PendingNormed:
+    """A sub-layer's output that still has to go through the norm that follows it (``norm.close(stream, delta)`` or the
+    next norm kernel on its way) before it is added to the residual stream."""
+
+    delta: torch.Tensor  # [T, W] in the compute dtype
+    norm: "Norm"
 
 
 @dataclass
@@ -383,11 +396,14 @@ class LayerCall:
 
     A layer may appear in several calls (shared weights), each with a cache of its own,
     or with ``write_cache=False`` on a cache that an earlier call filled (shared keys/values).
+    ``repeat``: which run of the layer this is (0 for the first); a block finds it in
+    ``ctx.per_step[LAYER_REPEAT]`` (a span of layers that runs several times and adds something else each time).
     """
 
     layer: int
     cache: Optional[int]
     write_cache: bool = True
+    repeat: int = 0
 
 
 @dataclass

@@ -1,6 +1,7 @@
 """The arrangements of norms, mixer and feed-forward around the residual stream: the norm before each
-sub-layer (``pre_norm``), the norm after each sub-layer's sum (``post_norm``), and the norm before each sub-layer
-of a model that keeps several residual streams per token (``hyper_pre_norm``, at the end of the file).
+sub-layer (``pre_norm``), the norm after each sub-layer's sum (``post_norm``), the norm before each sub-layer
+of a model that keeps several residual streams per token (``hyper_pre_norm``), and a norm on both sides of each
+sub-layer (``sandwich_norm``, at the end of the file).
 
 Pre-norm residual block: h = x + mixer(norm1(x)); y = h + feed_forward(norm2(h)).
 
@@ -19,8 +20,8 @@ import torch
 
 from ..registry import create_part, register_part
 from ..kernels import ops
-from .base import (EMBEDDING_OUTPUT, NEXT_NORM_WEIGHT, STREAM_SUMSQ, Block, PartSpec, PendingStreamWrite, Runtime, StateSpec, StepContext,
-                   WeightSpec)
+from .base import (EMBEDDING_OUTPUT, EMBEDDING_SIDE, LAYER_REPEAT, NEXT_NORM_WEIGHT, STREAM_SUMSQ, Block, PartSpec, PendingNormed,
+                   PendingStreamWrite, Runtime, StateSpec, StepContext, WeightSpec)
 from .linear import Linear
 
 
@@ -321,3 +322,118 @@ class HyperPreNormBlock(Block):
             y = self.feed_forward.forward(x)
             pending = PendingStreamWrite(y, self.coef[1][2], self.coef[1][1])
         return pending
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm before and a norm after each sub-layer:
+
+        x <- x + norm1b(mixer(norm1(x)));   x <- x + norm2b(feed_forward(norm2(x)))
+
+    The norms are parts with ``add_norm(stream, delta, extra_rows, extra_vec)`` and ``close(stream, delta, want_copy)``
+    (``dynamic_tanh``): the norm after a sub-layer, the sum into the float32 stream and the norm before the next
+    sub-layer are one pass over the stream.  ``feed_forward`` may be None (the block is then the mixer between its two
+    norms).  Two options, both off by default:
+
+    ``entry``: ``{"step": name of a tensor [times, width], "embedding": bool}``.  The block is the first of a span of
+    layers that runs ``times`` times; at the start of run t (``ctx.per_step[LAYER_REPEAT]``) the stream takes
+    ``step[t]`` and, from the second run on and if ``embedding`` is set, the embedding's output once more.  Both ride on
+    the block's first norm.
+    ``side``: ``{"column": c, "dim": d, "eps": e}`` and the tensors ``<name>.<side>.gate`` [d, width], ``.proj``
+    [width, d] and ``.norm`` [width].  After the block's last sub-layer the stream takes a term made from a second
+    embedding of the token, of whose row (``ctx.per_step[EMBEDDING_SIDE]``, looked up by the embedding part) the block
+    reads the columns c .. c + d - 1:
+
+        g = gelu_tanh(W_gate x) * row;   y = W_proj g;   x <- x + y / sqrt(mean(y^2) + e) * w_norm
+
+    Without ``side`` the block hands its last sub-layer's output on as ``PendingNormed`` (the next block's first norm,
+    or the model's last one, brings it through the norm after the sub-layer and into the stream)."""
+
+    def __init__(self, name: str, width: int, norm1: PartSpec, norm1b: PartSpec, mixer: PartSpec,
+                 norm2: Optional[PartSpec] = None, norm2b: Optional[PartSpec] = None, feed_forward: Optional[PartSpec] = None,
+                 entry: Optional[dict] = None, side: Optional[dict] = None, names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        n = {"norm1": "norm1", "norm1b": "norm1b", "mixer": "mixer", "norm2": "norm2", "norm2b": "norm2b",
+             "feed_forward": "feed_forward", "side": "side"}
+        n.update(names or {})
+        self.width = int(width)
+        if self.width <= 0:
+            raise ValueError(f"block {name}: needs the stream's width")
+        self.norm1 = create_part("norm", norm1, name=f"{name}.{n['norm1']}")
+        self.norm1b = create_part("norm", norm1b, name=f"{name}.{n['norm1b']}")
+        self.mixer = create_part("mixer", mixer, name=f"{name}.{n['mixer']}")
+        self.norm2 = self.norm2b = self.feed_forward = None
+        if feed_forward is not None:
+            if norm2 is None or norm2b is None:
+                raise ValueError(f"block {name}: a feed-forward needs the norms before and after it")
+            self.norm2 = create_part("norm", norm2, name=f"{name}.{n['norm2']}")
+            self.norm2b = create_part("norm", norm2b, name=f"{name}.{n['norm2b']}")
+            self.feed_forward = create_part("feed_forward", feed_forward, name=f"{name}.{n['feed_forward']}")
+        for norm in self._norms():
+            if not (hasattr(norm, "close") and hasattr(norm, "add_norm")):
+                raise ValueError(f"block {name}: {type(norm).__name__} cannot stand on both sides of a sub-layer")
+        self.entry = dict(entry) if entry else None
+        self.side = dict(side) if side else None
+        self.side_prefix = f"{name}.{n['side']}"
+        if self.side and (int(self.side["dim"]) <= 0 or int(self.side["column"]) < 0):
+            raise ValueError(f"block {name}: the token-side slice needs a width and a column")
+        self.needs_embedding_output = bool(self.entry and self.entry.get("embedding"))
+
+    def _norms(self):
+        return [p for p in (self.norm1, self.norm1b, self.norm2, self.norm2b) if p is not None]
+
+    def _parts(self):
+        return self._norms() + [p for p in (self.mixer, self.feed_forward) if p is not None]
+
+    @property
+    def graph_capturable(self) -> bool:
+        return all(p.graph_capturable for p in self._parts())
+
+    def weight_specs(self) -> List[WeightSpec]:
+        specs = [s for p in self._parts() for s in p.weight_specs()]
+        if self.side:
+            d = int(self.side["dim"])
+            specs += [WeightSpec(f"{self.side_prefix}.gate", (d, self.width)),
+                      WeightSpec(f"{self.side_prefix}.proj", (self.width, d)),
+                      WeightSpec(f"{self.side_prefix}.norm", (self.width,), kind="vector", init="one_plus_normal")]
+        if self.entry and self.entry.get("declares", True):
+            specs.append(WeightSpec(self.entry["step"], (int(self.entry["times"]), self.width), kind="vector", init="normal"))
+        return specs
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        for part in self._parts():
+            part.setup(rt, weights)
+        if self.side:
+            d = int(self.side["dim"])
+            self.side_gate = Linear(weights.pop(f"{self.side_prefix}.gate"), rt, tag="block.side_gate")
+            self.side_proj = Linear(weights.pop(f"{self.side_prefix}.proj"), rt, tag="block.side_proj")
+            self.side_norm = weights[f"{self.side_prefix}.norm"]
+            self._side_g = rt.shared("block.side_g", rt.max_tokens, d)
+        if self.entry:
+            self.entry_steps = weights[self.entry["step"]]  # [times, width], float32
+
+    def forward(self, stream: torch.Tensor, pending, ctx: StepContext, cache_id: Optional[int],
+                write_cache: bool):
+        shared = ctx.__dict__.setdefault("per_step", {})
+        extra_rows = extra_vec = None
+        if self.entry:
+            run = int(shared.get(LAYER_REPEAT, 0))
+            if not 0 <= run < self.entry_steps.shape[0]:
+                raise ValueError(f"block {self.name}: run {run} of a span that runs {self.entry_steps.shape[0]} times")
+            extra_vec = self.entry_steps[run]
+            if run > 0 and self.entry.get("embedding"):
+                extra_rows = shared[EMBEDDING_OUTPUT]
+        x = self.norm1.add_norm(stream, pending, extra_rows=extra_rows, extra_vec=extra_vec)
+        a = self.mixer.forward(x, ctx, cache_id, write_cache)
+        last, after = a, self.norm1b
+        if self.feed_forward is not None:
+            x = self.norm2.add_norm(stream, PendingNormed(a, self.norm1b))
+            last, after = self.feed_forward.forward(x), self.norm2b
+        if not self.side:
+            return PendingNormed(last, after)
+        x = after.close(stream, last, want_copy=True)
+        g = self._side_g[: stream.shape[0]]
+        ops.side_gate(self.side_gate(x), shared[EMBEDDING_SIDE], int(self.side["column"]), g)
+        ops.add_unit_rms(stream, self.side_proj(g), self.side_norm, float(self.side["eps"]))
+        return None

@@ -22,24 +22,42 @@ class TokenEmbedding(Part):
     graph_capturable = True
 
     def __init__(self, name: str, vocab_size: int, hidden_size: int, suffix: str = ".weight", scale: float = 1.0,
-                 copies: Optional[int] = None):
+                 copies: Optional[int] = None, side_table: Optional[str] = None, side_width: int = 0):
         """``suffix``: what follows the part's name in its tensor's name ("" for a tensor named like the part).
         ``scale`` multiplies the looked-up rows.  With ``copies`` (a number, 1 included) the model's blocks keep that
         many residual streams per token: the result is [T, copies, hidden], every stream starting as the same row;
-        None: the single stream [T, hidden] of the other blocks."""
+        None: the single stream [T, hidden] of the other blocks.  ``side_table``: the full name of a second table
+        [vocab, side_width] of the token, whose rows ``side_rows`` looks up once per step for the layers that read
+        their slice of it."""
         super().__init__(name)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.tensor = f"{name}{suffix}"
         self.scale, self.copies = float(scale), None if copies is None else int(copies)
+        self.side_table, self.side_width = side_table, int(side_width)
+        self.has_side_table = bool(side_table)
+        if self.has_side_table and self.side_width <= 0:
+            raise ValueError(f"embedding {name}: the second table needs its width")
         if self.copies is not None and not 1 <= self.copies <= ops.HC_MAX_STREAMS:
             raise ValueError(f"embedding {name}: between 1 and {ops.HC_MAX_STREAMS} residual streams, got {self.copies}")
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.tensor, (self.vocab_size, self.hidden_size))]
+        specs = [WeightSpec(self.tensor, (self.vocab_size, self.hidden_size))]
+        if self.has_side_table:
+            specs.append(WeightSpec(self.side_table, (self.vocab_size, self.side_width)))
+        return specs
+
+    def side_rows(self, token_ids: torch.Tensor) -> torch.Tensor:
+        """float32 [T, side_width]: the tokens' rows of the second table."""
+        rows = self._side[: token_ids.numel()]
+        ops.embed(self.side_weight, token_ids, rows, self.rt.status)
+        return rows
 
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
         self.weight = weights[self.tensor]
+        if self.has_side_table:
+            self.side_weight = weights[self.side_table]
+            self._side = rt.shared("embedding.side", rt.max_tokens, self.side_width, dtype=torch.float32)
         self.plain = self.copies is None and self.scale == 1.0
         shape = (rt.max_tokens, self.hidden_size) if self.copies is None else (rt.max_tokens, self.copies, self.hidden_size)
         self._stream = rt.shared("stream", *shape, dtype=torch.float32)

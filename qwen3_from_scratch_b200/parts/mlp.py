@@ -144,18 +144,26 @@ class RoutedExperts(FeedForward):
         chosen: the ``top`` experts with the largest s + correction (ties: the lower index)
         y = sum_chosen s_e * router_scale * expert_e(h)  [+ shared(h)]
 
+    ``gated=True``: the experts are gated, W_down (act(W_gate h) * (W_up h)), with a further tensor
+    ``<name>.<expert><e>.<gate>`` [ff, width].  ``weigh="input"``: the router's weight multiplies what the expert reads
+    instead of what it returns, y = sum_chosen expert_e(s_e * router_scale * h).
+
     The correction takes part in the choice only; the weights are not renormalised.  ``shared``: a feed-forward
     (any registered one) that every token goes through, added to the sum, or None.  Tensors: ``<name>.<router>``
     [E, width], ``<name>.<correction>`` [E] (absent with ``correction=False``), ``<name>.<expert><e>.<up>`` [ff, width]
     and ``.<down>`` [width, ff], and the shared part's under ``<name>.<shared>``."""
 
     graph_capturable = True
-    NAMES = {"router": "router", "correction": "correction", "expert": "e", "up": "up", "down": "down", "shared": "shared"}
+    NAMES = {"router": "router", "correction": "correction", "expert": "e", "up": "up", "down": "down", "gate": "gate",
+             "shared": "shared"}
 
     def __init__(self, name: str, hidden_size: int, experts: int, top: int, expert_ff: int, router_scale: float = 1.0,
                  activation: str = "relu_sq", correction: bool = True, shared: Optional[PartSpec] = None,
-                 names: Optional[Dict[str, str]] = None):
+                 names: Optional[Dict[str, str]] = None, gated: bool = False, weigh: str = "output"):
         super().__init__(name)
+        if weigh not in ("output", "input"):
+            raise ValueError(f"feed-forward {name}: the router's weight goes to an expert's 'input' or 'output', got {weigh!r}")
+        self.gated, self.weigh_input = bool(gated), weigh == "input"
         self.hidden_size, self.experts, self.top, self.expert_ff = int(hidden_size), int(experts), int(top), int(expert_ff)
         if not 1 <= self.top <= min(self.experts, ops.MOE_MAX_TOP):
             raise ValueError(f"feed-forward {name}: top {self.top} of {self.experts} experts (at most {ops.MOE_MAX_TOP})")
@@ -177,6 +185,8 @@ class RoutedExperts(FeedForward):
         if self.has_correction:
             specs.append(WeightSpec(f"{self.name}.{self.n['correction']}", (self.experts,), kind="vector", init="normal"))
         for e in range(self.experts):
+            if self.gated:
+                specs.append(WeightSpec(self._expert(e, "gate"), (f, w)))
             specs += [WeightSpec(self._expert(e, "up"), (f, w)), WeightSpec(self._expert(e, "down"), (w, f))]
         return specs + (self.shared.weight_specs() if self.shared is not None else [])
 
@@ -185,7 +195,16 @@ class RoutedExperts(FeedForward):
         self.router = weights[f"{self.name}.{self.n['router']}"]
         self.correction = weights[f"{self.name}.{self.n['correction']}"] if self.has_correction else None
         # the experts' matrices in two stacks, in the compute dtype: up [E, ff, width], down [E, width, ff]
-        self.up = torch.stack([weights.pop(self._expert(e, "up")).to(rt.dtype) for e in range(self.experts)]).contiguous()
+        self.gate_block = ops.moe_gate_block(self.expert_ff) if self.gated else 0
+        if self.gated:
+            # gate and up rows of an expert alternate in blocks of gate_block rows: [E, 2 ff, width]
+            gb, f, w = self.gate_block, self.expert_ff, self.hidden_size
+            self.up = torch.stack([
+                torch.cat([weights.pop(self._expert(e, "gate")).to(rt.dtype).view(f // gb, gb, w),
+                           weights.pop(self._expert(e, "up")).to(rt.dtype).view(f // gb, gb, w)], dim=1).reshape(2 * f, w)
+                for e in range(self.experts)]).contiguous()
+        else:
+            self.up = torch.stack([weights.pop(self._expert(e, "up")).to(rt.dtype) for e in range(self.experts)]).contiguous()
         self.down = torch.stack([weights.pop(self._expert(e, "down")).to(rt.dtype) for e in range(self.experts)]).contiguous()
         if self.shared is not None:
             self.shared.setup(rt, weights)
@@ -196,7 +215,9 @@ class RoutedExperts(FeedForward):
         self._out = rt.shared("moe.out", T, self.hidden_size)
         self._status = rt.status
         self._grouped = None
-        if ops.moe_grouped_takes(rt.dtype, self.hidden_size, self.expert_ff):
+        # a design that weighs the experts' input adds their outputs up as they are
+        self._ones = torch.ones(T, self.top, dtype=torch.float32, device=rt.device) if self.weigh_input else None
+        if ops.moe_grouped_takes(rt.dtype, self.hidden_size, self.expert_ff, gated=self.gated):
             self._grouped = ops.MoeScratch(rt.shared, T, self.top, self.experts, self.hidden_size, self.expert_ff)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -205,6 +226,7 @@ class RoutedExperts(FeedForward):
         ops.moe_route(x, self.router, self.correction, ids, wts, self.router_scale)
         base = self.shared.forward(x) if self.shared is not None else None
         out = self._out[:T]
-        ops.routed_experts(x, self.up, self.down, ids, wts, base, self._act[: T * self.top], out, self.activation,
-                           scratch=self._grouped, status=self._status)
+        ops.routed_experts(x, self.up, self.down, ids, self._ones[:T] if self.weigh_input else wts, base,
+                           self._act[: T * self.top], out, self.activation, scratch=self._grouped, status=self._status,
+                           gate_block=self.gate_block, in_weights=wts if self.weigh_input else None)
         return out

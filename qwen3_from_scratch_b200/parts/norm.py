@@ -1,4 +1,5 @@
-"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, and layer norm with weight and bias; statistics in float32.
+"""RMSNorm: y = x / sqrt(mean(x^2) + eps) * w, and layer norm with weight and bias; statistics in float32.  And Dynamic
+Tanh, which stands where a norm stands but computes no statistics: y = tanh(alpha x) w + b.
 
 Reference: models/norm.py:11-22 (weight multiplies directly, eps from the configuration),
 csrc/rms_norm/rms_norm.cpp:13-31.
@@ -12,7 +13,7 @@ import torch
 
 from ..kernels import ops
 from ..registry import register_part
-from .base import Norm, Runtime, StreamNorm, StreamStats, WeightSpec
+from .base import Norm, PendingNormed, Runtime, StreamNorm, StreamStats, WeightSpec
 
 
 @register_part("norm", "rms_norm")
@@ -147,4 +148,76 @@ class LayerNorm(Norm):
     def norm_rows(self, stream: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor) -> torch.Tensor:
         out = torch.empty(rows.numel(), self.dim, dtype=self.rt.dtype, device=stream.device)
         ops.add_layernorm(stream, delta, self.weight, self.bias, out, self.eps, rows=rows)
+        return out
+
+
+@register_part("norm", "dynamic_tanh")
+class DynamicTanh(Norm):
+    """y = tanh(alpha x) w + b over the last axis, with one learned scalar alpha, a weight and a bias per feature: the
+    stand-in for a norm of Zhu et al., "Transformers without Normalization".  Nothing is reduced over the row.  The
+    weight is the tensor ``<name><suffix>``, the bias ``<name><bias_suffix>``, alpha ``<name><alpha_suffix>`` (no
+    dimensions).  All float32.
+
+    ``delta`` may be a tensor (added as it is) or a ``PendingNormed`` (a sub-layer's output that first goes through the
+    Dynamic Tanh that follows the sub-layer): both in the same pass over the stream as this norm.  ``extra_rows``
+    (float32 [T, dim]) and ``extra_vec`` (float32 [dim]) are added to the stream on the same pass."""
+
+    graph_capturable = True
+
+    def __init__(self, name: str, dim: int, suffix: str = ".weight", bias_suffix: str = ".bias", alpha_suffix: str = ".alpha"):
+        super().__init__(name)
+        self.dim = int(dim)
+        self.tensor, self.bias_tensor, self.alpha_tensor = f"{name}{suffix}", f"{name}{bias_suffix}", f"{name}{alpha_suffix}"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.tensor, (self.dim,), kind="vector", init="one_plus_normal"),
+                WeightSpec(self.bias_tensor, (self.dim,), kind="vector", init="normal"),
+                WeightSpec(self.alpha_tensor, (), kind="vector", init="one_plus_normal")]
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        self.weight, self.bias = weights[self.tensor], weights[self.bias_tensor]
+        self.alpha = weights[self.alpha_tensor].reshape(1)
+        self._out = rt.shared("normed", rt.max_tokens, self.dim)
+
+    @property
+    def params(self):
+        return (self.alpha, self.weight, self.bias)
+
+    @staticmethod
+    def _open(delta):
+        """(tensor or None, the Dynamic Tanh it still has to go through or None)."""
+        if isinstance(delta, PendingNormed):
+            if not isinstance(delta.norm, DynamicTanh):
+                raise ValueError(f"the open sub-layer output waits for {type(delta.norm).__name__}, which this norm's kernel "
+                                 f"does not apply")
+            return delta.delta, delta.norm.params
+        return delta, None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        stream = x.to(torch.float32).contiguous()
+        out = torch.empty(x.shape, dtype=self.rt.dtype, device=x.device)
+        ops.add_dyt(stream.view(-1, self.dim), None, None, self.params, out.view(-1, self.dim))
+        return out
+
+    def add_norm(self, stream: torch.Tensor, delta, extra_rows: Optional[torch.Tensor] = None,
+                 extra_vec: Optional[torch.Tensor] = None) -> torch.Tensor:
+        out = self._out[: stream.shape[0]]
+        d, after = self._open(delta)
+        ops.add_dyt(stream, d, after, self.params, out, rows_add=extra_rows, vec_add=extra_vec)
+        return out
+
+    def close(self, stream: torch.Tensor, delta: torch.Tensor, want_copy: bool = False) -> Optional[torch.Tensor]:
+        """stream += this(delta), with no norm after it; ``want_copy``: the new rows in the compute dtype (in a float32
+        run the stream itself)."""
+        out = None
+        if want_copy and self.rt.dtype != torch.float32:
+            out = self._out[: stream.shape[0]]
+        ops.add_dyt(stream, delta, self.params, None, out)
+        return (stream if out is None else out) if want_copy else None
+
+    def norm_rows(self, stream: torch.Tensor, delta, rows: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(rows.numel(), self.dim, dtype=self.rt.dtype, device=stream.device)
+        d, after = self._open(delta)
+        ops.add_dyt(stream, d, after, self.params, out, rows=rows)
         return out

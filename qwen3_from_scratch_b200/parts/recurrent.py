@@ -10,7 +10,11 @@
                     step = softplus(W_dt dt + b); S[c, n] = exp(step_c A[c, n]) S[c, n] + step_c x_c B_n;
                     y_c = sum_n S[c, n] C_n + D_c x_c; out = W_o (y * silu(z)).
 
-Both keep two things per request, named in ``cache_spec()``: ``state`` (float32) and ``conv`` (the last
+``mlstm``           the matrix memory of the xLSTM (Beck et al., "xLSTM: Extended Long Short-Term Memory"): per head a
+                    memory S [dim, vdim] with exponential input and forget gates kept stable by a running maximum
+                    (see the class).
+
+The first two keep two things per request, named in ``cache_spec()``: ``state`` (float32) and ``conv`` (the last
 taps - 1 inputs of the short convolution, float32).  A new request's slot is zero.  The projections are
 ``Linear``s (the compute dtype, float32 accumulation); decays, step sizes, gates and the state are float32 in
 every run; a portion of a prompt is walked token by token in the same order as the whole prompt.
@@ -321,6 +325,96 @@ class MinGRU(Mixer, _NamedTensors):
         ops.mingru_scan(proj, column, column + c, column + 2 * c, self.z_bias, self.x_bias, ctx.state(cache_id),
                         ctx.q_start, ctx.slot_ids, ctx.num_seqs, out, out_scale, self.rt.status, max_q_len=ctx.max_q_len,
                         scratch=self._chunks)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
+        gated = self._gated[: x.shape[0]]
+        self.core(self.in_proj(x), 0, ctx, cache_id, write_cache, gated, 1.0)
+        return self.out_proj(gated)
+
+
+@register_part("mixer", "mlstm")
+class MLSTM(Mixer, _NamedTensors):
+    """The mLSTM cell.  With h the input, H heads, keys of ``dim`` and values of ``vdim`` values:
+
+        q = W_q h * dim^-1/2;  k = W_k h;  v = W_v h
+        i = cap tanh((W_i h + b_i) / cap);   f = logsigmoid(cap tanh((W_f h + b_f) / cap))        (log gates, per head)
+        m' = max(f + m, i);   S' = exp(f + m - m') S + exp(i - m') k v^T;   n' = exp(f + m - m') n + exp(i - m') k
+        o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
+        out = W_o (unit_rms_per_head(o) * norm * sigmoid(W_g h))
+
+    S, n and m start at zero for a new request and are float32 (``memory``, ``normaliser``, ``maximum`` in the cache
+    needs); gates, decays and the division are float32 in every run.  ``names``: the tensors' names after the part's
+    own."""
+
+    graph_capturable = True
+    splittable = True
+    NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "i": "i", "i_bias": "i.b", "f": "f", "f_bias": "f.b", "norm": "norm",
+             "out": "o"}
+
+    def __init__(self, name: str, hidden_size: int, num_heads: int, dim: int, vdim: int, gate_cap: float, norm_eps: float,
+                 names: Optional[Dict[str, str]] = None):
+        super().__init__(name)
+        self.hidden_size, self.num_heads, self.dim, self.vdim = int(hidden_size), int(num_heads), int(dim), int(vdim)
+        self.gate_cap, self.norm_eps = float(gate_cap), float(norm_eps)
+        if self.gate_cap <= 0:
+            raise ValueError(f"mixer {name}: the gates' cap must be positive, got {self.gate_cap}")
+        self._name_tensors(name, self.NAMES, names)
+
+    def weight_specs(self) -> List[WeightSpec]:
+        t, w, H, D, Dv = self.tensors, self.hidden_size, self.num_heads, self.dim, self.vdim
+        return [WeightSpec(t["q"], (H * D, w)), WeightSpec(t["k"], (H * D, w)), WeightSpec(t["v"], (H * Dv, w)),
+                WeightSpec(t["gate"], (H * Dv, w)), WeightSpec(t["i"], (H, w)), WeightSpec(t["f"], (H, w)),
+                WeightSpec(t["i_bias"], (H,), kind="vector", init="normal"),
+                WeightSpec(t["f_bias"], (H,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["norm"], (H * Dv,), kind="vector", init="one_plus_normal"),
+                WeightSpec(t["out"], (w, H * Dv))]
+
+    def cache_spec(self):
+        H, D, Dv = self.num_heads, self.dim, self.vdim
+        return {"memory": StateSpec((H, D, Dv), "float32"), "normaliser": StateSpec((H, D), "float32"),
+                "maximum": StateSpec((H,), "float32")}
+
+    def input_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        t = self.tensors
+        parts = [weights.pop(t[k]) for k in ("q", "k", "v", "gate", "i", "f")]
+        dtype = torch.float32 if any(p.dtype == torch.float32 for p in parts) else parts[0].dtype
+        rows = sum(p.shape[0] for p in parts)
+        pad = torch.zeros((-rows) % 8, parts[0].shape[1], dtype=dtype, device=parts[0].device)  # whole groups of eight rows
+        return torch.cat([p.to(dtype) for p in parts] + [pad], dim=0)  # columns of the product: q, k, v, g, i, f
+
+    def output_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
+        return weights.pop(self.tensors["out"])
+
+    @property
+    def output_columns(self) -> int:
+        return self.num_heads * self.vdim
+
+    def setup_core(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        self.rt = rt
+        if self.dim > ops.mlstm_max_dim():
+            raise ValueError(f"mixer {self.name}: keys of {self.dim} values exceed the {ops.mlstm_max_dim()} the scan takes")
+        t = self.tensors
+        self.i_bias, self.f_bias, self.norm_weight = weights[t["i_bias"]], weights[t["f_bias"]], weights[t["norm"]]
+        self._h = rt.shared("mlstm.h", rt.max_tokens, self.output_columns, dtype=torch.float32)
+
+    def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
+        super().setup(rt, weights)
+        self.in_proj = Linear(self.input_weight(weights), rt, tag="mlstm.in")
+        self.out_proj = Linear(self.output_weight(weights), rt, tag="mlstm.out")
+        self.setup_core(rt, weights)
+        self._gated = rt.shared("mlstm.gated", rt.max_tokens, self.output_columns)
+
+    def core(self, proj: torch.Tensor, column: int, ctx: StepContext, cache_id: Optional[int], write_cache: bool,
+             out: torch.Tensor, out_scale: float) -> None:
+        H, D, Dv = self.num_heads, self.dim, self.vdim
+        q_col, k_col, v_col = column, column + H * D, column + 2 * H * D
+        g_col = v_col + H * Dv
+        i_col = g_col + H * Dv
+        h = self._h[: proj.shape[0]]
+        ops.mlstm_scan(proj, q_col, k_col, v_col, i_col, i_col + H, self.i_bias, self.f_bias, self.gate_cap,
+                       ctx.state(cache_id, "memory"), ctx.state(cache_id, "normaliser"), ctx.state(cache_id, "maximum"),
+                       ctx.q_start, ctx.slot_ids, ctx.num_seqs, h, self.rt.status)
+        ops.mlstm_out(h, proj, g_col, self.norm_weight, self.norm_eps, out, out_scale, H)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:
         gated = self._gated[: x.shape[0]]

@@ -106,4 +106,4 @@ def _load_builtin() -> None:
     if not _builtin_loaded:
         _builtin_loaded = True
         from .parts import attention, block, embedding, mlp, norm, parallel, recurrent, rope  # noqa: F401  register themselves
-        from .models import bikadra, binupel, dogidra, qwen3  # noqa: F401  register the architectures
+        from .models import bikadra, binupel, dogidra, qwen3, zasalix  # noqa: F401  register the architectures
