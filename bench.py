@@ -765,7 +765,7 @@ def main() -> int:
     p.add_argument("--only-rows", type=int, default=None, help="with --profile products: one number of rows")
     p.add_argument("--leave-out", action="store_true",
                    help="with --profile: time the step as a CUDA graph, whole and with each kind of kernel left out")
-    p.add_argument("--arch", choices=["binupel", "bikadra", "dogidra"], default=None,
+    p.add_argument("--arch", choices=["binupel", "bikadra", "dogidra", "zasalix"], default=None,
                    help="instead of the default workload: that design beside Qwen3 at equal layer sizes (a prompt step "
                         "and two decode batches, every kernel of a step timed on its own); see bench_arch.py")
     p.add_argument("--arch-size", default="2k", choices=["2k", "4k"], help="with --arch: the layer sizes")

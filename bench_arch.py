@@ -1,4 +1,5 @@
-"""``bench.py --arch binupel|bikadra|dogidra``: another design beside Qwen3 at equal layer sizes (random weights drawn on
+"""``bench.py --arch binupel|bikadra|dogidra|zasalix``: another design beside Qwen3 (Zasalix: beside Dogidra, the closest
+of the other designs) at equal layer sizes (random weights drawn on
 the device): a prompt step of 2,048 tokens and decode steps at two batch sizes, each replayed on the device
 between CUDA events, and every kernel of one eagerly launched step timed by events of its own, with the bytes
 or flops it must move and the fraction of the measured copy bandwidth or bf16 throughput that this makes.
@@ -6,7 +7,9 @@ or flops it must move and the fraction of the measured copy bandwidth or bf16 th
 A Binupel model of ``layers`` entries repeats the pattern selective scan, RG-LRU, attention; a Bikadra model
 alternates the state-space mixer and attention through a latent, over four residual streams; a Dogidra model runs
 windowed attention over pooled blocks beside a minGRU in every layer, routed experts with a shared one behind them,
-and a span of two layers twice; the Qwen3 model has as many layer runs of the same width, heads, head size and
+and a span of two layers twice; a Zasalix model repeats the pattern latent attention with a dense feed-forward, windowed
+attention that keeps the first tokens beside a matrix memory with routed gated experts, a matrix memory alone with
+routed gated experts, the last two as a span that runs twice; the Qwen3 model has as many layer runs of the same width, heads, head size and
 (active) feed-forward width.
 """
 
@@ -74,6 +77,31 @@ def dogidra_config(s):
     return {"architecture": "Dogidra", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0},
             "norm": {"eps": 1e-6}, "canon": {"taps": 4}, "loop": {"start": 1, "stop": 3, "times": 2},
             "layers": [layer] * (s["layers"] - 2)}
+
+
+def zasalix_config(s):
+    """Layer runs as in the other models: latent attention (a latent of 512 with a rotated part of 64, as the Bikadra
+    model's) with a dense feed-forward; windowed attention (1,024 tokens, the first 64 kept, as wide as the Dogidra
+    model's) beside a matrix memory with keys of 128 and values of 256 per head; a matrix memory alone, twice as many
+    heads; the last two kinds with 16 gated experts of a quarter of the dense width, three per token, and a shared
+    one.  The listed layers are runs - 2; layers 1 and 2 run twice."""
+    mem = lambda heads: {"heads": heads, "dim": 128, "vdim": 256, "gate_cap": 15.0}  # noqa: E731
+    moe = {"kind": "moe", "router": {"experts": 16, "top": 3}, "expert": {"ff": s["ff"] // 4}, "shared": {"ff": s["ff"] // 4}}
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": s["heads"], "dim": s["dim"], "rot_dim": 64, "vdim": s["dim"], "kv_rank": 512,
+                     "q_rank": 3 * s["width"] // 4, "scale": (s["dim"] + 64) ** -0.5, "rot": {"base": 10000.0, "dims": 64}},
+           "mlp": {"kind": "dense", "ff": s["ff"]}}
+    par = {"type": "parallel",
+           "mixer": {"left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                              "scale": s["dim"] ** -0.5, "mask": {"size": 1024, "keep_first": 64},
+                              "rot": {"base": 10000.0, "dims": s["dim"] // 2}},
+                     "right": mem(s["width"] // 512), "left_scale": 0.7, "right_scale": 0.7},
+           "mlp": moe}
+    rec = {"type": "mlstm", "mixer": mem(s["width"] // 256), "mlp": moe}
+    pattern = [lat, par, rec]
+    return {"architecture": "Zasalix", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "token_side": {"dim": 64}, "loop": {"start": 1, "stop": 3, "times": 2},
+            "layers": [pattern[i % 3] for i in range(s["layers"] - 2)]}
 
 
 def qwen3_config(s):
@@ -186,7 +214,29 @@ class KernelClock:
             return "bytes", size(a[0]) + size(a[1])
         if name == "latent_kv_post":
             proj, c_pages, r_pages, cq, gate = a[0], a[16], a[17], a[18], a[19]
-            return "bytes", size(proj) + size(cq) + size(gate) + proj.shape[0] * (c_pages.shape[3] + r_pages.shape[3]) * 2
+            return "bytes", (size(proj) + size(cq) + (size(gate) if gate is not None else 0)
+                             + proj.shape[0] * (c_pages.shape[3] + r_pages.shape[3]) * 2)
+        if name == "add_dyt":
+            stream, delta, out = a[0], a[1], a[4]
+            n = size(stream) * (2 if (delta is not None or k.get("rows_add") is not None or k.get("vec_add") is not None) else 1)
+            n += size(k["rows_add"]) if k.get("rows_add") is not None else 0
+            return "bytes", n + (size(delta) if delta is not None else 0) + (size(out) if out is not None else 0)
+        if name == "add_unit_rms":
+            return "bytes", 2 * size(a[0]) + size(a[1])
+        if name == "side_gate":
+            return "bytes", 2 * size(a[0]) + a[0].numel() * 4
+        if name == "sigmoid_gate":
+            x = a[0]
+            return "bytes", 3 * x.numel() * x.element_size()
+        if name == "mlstm_scan":
+            # what the walk must move: q, k, v and the result once, and the state in and out; against the copy bandwidth
+            memory, out = a[9], a[15]
+            H, D, Dv = memory.shape[1], memory.shape[2], memory.shape[3]
+            seqs = 1 if sc["kind"] == "prefill" else sc["batch"]
+            return "bytes", out.shape[0] * H * (2 * D + Dv) * a[0].element_size() + size(out) + 2 * seqs * H * D * Dv * 4
+        if name == "mlstm_out":
+            o, out = a[0], a[5]
+            return "bytes", size(o) + 2 * out.numel() * out.element_size()
         if name == "latent_q_post":
             return "bytes", 2 * size(a[0])
         if name == "gate_heads":
@@ -228,7 +278,9 @@ class KernelClock:
             q, k_pages, v_pages, window, pool = a[0], a[1], a[2], a[9], a[10]
             H, D = q.shape[1], q.shape[2]
             G, Dv = k_pages.shape[1], v_pages.shape[3]
-            seen = lambda i: min(i + 1, window) + max(0, i + 1 - window) // pool  # noqa: E731
+            limit = k.get("block_limit", -1)
+            blocks = lambda i: max(0, i + 1 - window) // pool  # noqa: E731
+            seen = lambda i: min(i + 1, window) + (blocks(i) if limit < 0 else min(blocks(i), limit))  # noqa: E731
             if sc["kind"] == "prefill":
                 return "flops", 2 * H * (D + Dv) * sum(seen(i) for i in range(sc["tokens"]))
             return "bytes", sc["batch"] * seen(sc["context"] - 1) * G * (D + Dv) * k_pages.element_size() + 2 * size(q)
@@ -243,7 +295,7 @@ class KernelClock:
             # the experts' matrices that the step touches (at most all of them) or the products, whichever takes
             # longer at 240 bf16 flops per byte of HBM (about the ratio of the two measured peaks)
             touched = min(pairs, up.shape[0]) * (size(up) + size(down)) // up.shape[0]
-            flops = 4 * pairs * up.shape[1] * up.shape[2]
+            flops = (6 if k.get("gate_block") else 4) * pairs * down.shape[2] * up.shape[2]
             return ("bytes", touched) if touched * 240 > flops else ("flops", flops)
         return "bytes", 0
 
@@ -271,7 +323,8 @@ class KernelClock:
                      "gemm_skinny_into_stream", "gemm_tc", "embed_scaled", "hc_norm", "act", "latent_kv_post",
                      "latent_q_post", "gate_heads", "latent_attention", "ssd_scan", "gated_group_norm", "add_layernorm",
                      "add_layernorm_conv1", "input_conv", "stream_concat", "pw_qkv_post", "pool_blocks", "pooled_window_attention",
-                     "mingru_scan", "moe_route", "routed_experts"):
+                     "mingru_scan", "moe_route", "routed_experts", "add_dyt", "add_unit_rms", "side_gate", "sigmoid_gate",
+                     "mlstm_scan", "mlstm_out"):
             self.wrap(ops, name, name)
         real_mm = torch.mm
         clock = self
@@ -358,13 +411,17 @@ def compare(args, peaks, sample_clocks):
                  "decode_b64_ctx2048": {"kind": "decode", "batch": 64, "context": 2048}}
     sampler = sample_clocks()
     t0 = time.time()
-    other = {"binupel": binupel_config, "bikadra": bikadra_config, "dogidra": dogidra_config}[args.arch]
-    out = {"arch": args.arch, "beside": "qwen3", "sizes": dict(size, name=args.arch_size), "dtype": "bf16",
+    other = {"binupel": binupel_config, "bikadra": bikadra_config, "dogidra": dogidra_config,
+             "zasalix": zasalix_config}[args.arch]
+    # what the design stands beside: Qwen3, or for Zasalix the closest of the other designs (a windowed attention
+    # beside a recurrence, routed experts, a span of layers that runs twice)
+    beside, beside_config = ("dogidra", dogidra_config) if args.arch == "zasalix" else ("qwen3", qwen3_config)
+    out = {"arch": args.arch, "beside": beside, "sizes": dict(size, name=args.arch_size), "dtype": "bf16",
            "data": "synthetic tokens, random weights drawn on the device", "steps": args.steps, "warmup": args.warmup,
            "peaks": peaks, "timing": "CUDA events around each replay of the step; 256 MB written between replays",
-           args.arch: {}, "qwen3": {}}
+           args.arch: {}, beside: {}}
     for name, scenario in scenarios.items():
-        for model, config in ((args.arch, other(size)), ("qwen3", qwen3_config(size))):
+        for model, config in ((args.arch, other(size)), (beside, beside_config(size))):
             out[model][name] = run_scenario(config, scenario, args.steps, args.warmup, peaks)
             print(f"[bench] {model} {name}: {out[model][name]['ms_per_step']} ms", file=sys.stderr, flush=True)
     out["clocks"] = sampler.stop()

@@ -18,7 +18,7 @@
 
 namespace q3 {
 
-constexpr int PW_PER = 8;  // values per lane: head sizes up to 256
+constexpr int PW_PER = 16;  // values per lane: head sizes up to 512
 
 // proj: [T, ld]: q (H * D values) at column 0, k (G * D) at k_col, v (G * Dv) at v_col.
 template <typename T>

@@ -167,7 +167,7 @@ class SafetensorsWriter:
             raise SafetensorsError(
                 f"expected '{want_name}' {shape} {dtype} next, got '{name}' {tuple(tensor.shape)} {tensor.dtype}")
         data = tensor.detach().cpu().contiguous()
-        raw = data.view(torch.uint8) if data.numel() else data
+        raw = data.reshape(-1).view(torch.uint8) if data.numel() else data  # reshape: a tensor without dimensions has no bytes view
         self._file.write(raw.numpy().tobytes() if raw.numel() else b"")
         self._next += 1
 
