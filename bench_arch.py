@@ -240,7 +240,7 @@ class KernelClock:
         if name == "latent_q_post":
             return "bytes", 2 * size(a[0])
         if name == "gate_heads":
-            return "bytes", size(a[0]) + size(a[1]) + size(a[2])
+            return "bytes", size(a[0]) + (size(a[1]) if a[1] is not None else 0) + size(a[2])
         if name == "latent_attention":
             q_abs, q_rot, c_pages = a[0], a[1], a[2]
             H, _, rank = q_abs.shape

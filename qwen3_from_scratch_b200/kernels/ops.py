@@ -181,7 +181,7 @@ _SIGNATURES = {
     "q3_sigmoid_gate": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "q3_mlstm_scan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_float, _c_void_p,
                       _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                      _c_void_p, _c_void_p],
+                      _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "q3_mlstm_out": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_float, _c_float, _c_void_p, _c_int, _c_int, _c_int,
                      _c_int, _c_int, _c_void_p],
 }
@@ -2276,13 +2276,39 @@ def mlstm_max_dim() -> int:
     return _DEVICE_FACTS["mlstm max dim"]
 
 
+MLSTM_SEGMENT = 128       # tokens of a segment of the segmented scan
+MLSTM_SEGMENTED_FROM = 256  # the longest portion of a step from which the segments pay
+
+
+def mlstm_segmented_pays(dtype: torch.dtype, max_q_len: int) -> bool:
+    """Whether a step runs the scan in segments side by side: bfloat16 (the float32 run keeps the single walk, whose sums
+    have one order whatever the cut) and a portion long enough to be cut."""
+    return dtype == torch.bfloat16 and max_q_len >= MLSTM_SEGMENTED_FROM
+
+
+class MlstmScratch:
+    """What the segmented scan of at most ``max_tokens`` tokens of ``max_seqs`` requests keeps between its kernels."""
+
+    def __init__(self, alloc, max_tokens: int, max_seqs: int, heads: int, dim: int, vdim: int):
+        self.max_segments = max_tokens // MLSTM_SEGMENT + max_seqs
+        n = self.max_segments
+        self.segments = alloc("mlstm.segments", n * 4, dtype=torch.int32)
+        self.first_of = alloc("mlstm.first_of", max_seqs + 1, dtype=torch.int32)
+        self.memory = alloc("mlstm.seg_memory", n * heads * vdim * dim, dtype=torch.float32)
+        self.normaliser = alloc("mlstm.seg_normaliser", n * heads * dim, dtype=torch.float32)
+        self.maxima = alloc("mlstm.seg_maxima", 3 * n * heads, dtype=torch.float32)
+
+
 def mlstm_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, i_col: int, f_col: int, i_bias: torch.Tensor,
                f_bias: torch.Tensor, cap: float, memory: torch.Tensor, normaliser: torch.Tensor, maximum: torch.Tensor,
-               q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor, status: torch.Tensor) -> None:
+               q_start: torch.Tensor, slot_ids: torch.Tensor, num_seqs: int, out: torch.Tensor, status: torch.Tensor,
+               max_q_len: int = 1, scratch: Optional[MlstmScratch] = None) -> None:
     """The mLSTM recurrence over every request's tokens in order.  ``proj`` [T, any]: q and k (heads * dim each), v
     (heads * vdim) and the two gates' pre-activations (heads each) from the given columns; state per slot: ``memory``
-    [slots, heads, dim, vdim], ``normaliser`` [slots, heads, dim], ``maximum`` [slots, heads], float32, read and
-    renewed; ``out`` float32 [T, heads * vdim]: S^T q / (max(|n . q|, exp(-m)) + 1e-6) with q times dim^-1/2."""
+    [slots, heads, vdim, dim] (the memory column by column), ``normaliser`` [slots, heads, dim], ``maximum`` [slots, heads], float32, read and
+    renewed; ``out`` float32 [T, heads * vdim]: S^T q / (max(|n . q|, exp(-m)) + 1e-6) with q times dim^-1/2.  With
+    ``scratch`` and a step for which ``mlstm_segmented_pays``, every portion is cut into segments that are walked side
+    by side (each from an empty memory, then a carry through a request's segments, then the walk that writes)."""
     _check("mlstm_scan.proj", proj)
     for name, t in (("i_bias", i_bias), ("f_bias", f_bias), ("memory", memory), ("normaliser", normaliser),
                     ("maximum", maximum), ("out", out)):
@@ -2290,16 +2316,24 @@ def mlstm_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, i_col: in
     for name, t in (("q_start", q_start), ("slot_ids", slot_ids)):
         _check(f"mlstm_scan.{name}", t, torch.int32)
     T, ld = proj.shape
-    slots, H, D, Dv = memory.shape
+    slots, H, Dv, D = memory.shape
     if (tuple(normaliser.shape) != (slots, H, D) or tuple(maximum.shape) != (slots, H) or tuple(out.shape) != (T, H * Dv)
             or i_bias.numel() != H or f_bias.numel() != H or min(q_col, k_col, v_col, i_col, f_col) < 0
             or max(q_col + H * D, k_col + H * D, v_col + H * Dv, i_col + H, f_col + H) > ld):
         raise KernelError(f"mlstm_scan: proj {tuple(proj.shape)}, memory {tuple(memory.shape)}, out {tuple(out.shape)}")
+    seg, max_segments, extra = 0, 0, [None] * 5
+    if scratch is not None and mlstm_segmented_pays(proj.dtype, max_q_len):
+        seg, max_segments = MLSTM_SEGMENT, T // MLSTM_SEGMENT + int(num_seqs)
+        if (max_segments > scratch.max_segments or scratch.memory.numel() < max_segments * H * Dv * D
+                or scratch.first_of.numel() < num_seqs + 1):
+            raise KernelError(f"mlstm_scan: the scratch holds {scratch.max_segments} segments, the step needs {max_segments}")
+        extra = [scratch.segments.data_ptr(), scratch.first_of.data_ptr(), scratch.memory.data_ptr(),
+                 scratch.normaliser.data_ptr(), scratch.maxima.data_ptr()]
     code = library().q3_mlstm_scan(proj.data_ptr(), ld, int(q_col), int(k_col), int(v_col), int(i_col), int(f_col),
                                    i_bias.data_ptr(), f_bias.data_ptr(), float(cap), memory.data_ptr(),
                                    normaliser.data_ptr(), maximum.data_ptr(), q_start.data_ptr(), slot_ids.data_ptr(),
-                                   slots, out.data_ptr(), dtype_tag(proj.dtype), int(num_seqs), H, D, Dv,
-                                   status.data_ptr(), _stream())
+                                   slots, out.data_ptr(), dtype_tag(proj.dtype), int(num_seqs), H, D, Dv, seg, max_segments,
+                                   *extra, status.data_ptr(), _stream())
     _done("mlstm_scan", code, f"heads {H}, dim {D}, vdim {Dv}")
 
 

@@ -342,8 +342,8 @@ class MLSTM(Mixer, _NamedTensors):
         o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
         out = W_o (unit_rms_per_head(o) * norm * sigmoid(W_g h))
 
-    S, n and m start at zero for a new request and are float32 (``memory``, ``normaliser``, ``maximum`` in the cache
-    needs); gates, decays and the division are float32 in every run.  ``names``: the tensors' names after the part's
+    S, n and m start at zero for a new request and are float32 (``memory``, kept as S^T, ``normaliser``, ``maximum`` in
+    the cache needs); gates, decays and the division are float32 in every run.  ``names``: the tensors' names after the part's
     own."""
 
     graph_capturable = True
@@ -371,7 +371,8 @@ class MLSTM(Mixer, _NamedTensors):
 
     def cache_spec(self):
         H, D, Dv = self.num_heads, self.dim, self.vdim
-        return {"memory": StateSpec((H, D, Dv), "float32"), "normaliser": StateSpec((H, D), "float32"),
+        # the memory column by column ([vdim, dim]): the lanes that share a column read consecutive floats
+        return {"memory": StateSpec((H, Dv, D), "float32"), "normaliser": StateSpec((H, D), "float32"),
                 "maximum": StateSpec((H,), "float32")}
 
     def input_weight(self, weights: Dict[str, torch.Tensor]) -> torch.Tensor:
@@ -396,6 +397,9 @@ class MLSTM(Mixer, _NamedTensors):
         t = self.tensors
         self.i_bias, self.f_bias, self.norm_weight = weights[t["i_bias"]], weights[t["f_bias"]], weights[t["norm"]]
         self._h = rt.shared("mlstm.h", rt.max_tokens, self.output_columns, dtype=torch.float32)
+        self._segments = None
+        if ops.mlstm_segmented_pays(rt.dtype, rt.max_tokens):
+            self._segments = ops.MlstmScratch(rt.shared, rt.max_tokens, rt.max_seqs, self.num_heads, self.dim, self.vdim)
 
     def setup(self, rt: Runtime, weights: Dict[str, torch.Tensor]) -> None:
         super().setup(rt, weights)
@@ -413,7 +417,8 @@ class MLSTM(Mixer, _NamedTensors):
         h = self._h[: proj.shape[0]]
         ops.mlstm_scan(proj, q_col, k_col, v_col, i_col, i_col + H, self.i_bias, self.f_bias, self.gate_cap,
                        ctx.state(cache_id, "memory"), ctx.state(cache_id, "normaliser"), ctx.state(cache_id, "maximum"),
-                       ctx.q_start, ctx.slot_ids, ctx.num_seqs, h, self.rt.status)
+                       ctx.q_start, ctx.slot_ids, ctx.num_seqs, h, self.rt.status, max_q_len=ctx.max_q_len,
+                       scratch=self._segments)
         ops.mlstm_out(h, proj, g_col, self.norm_weight, self.norm_eps, out, out_scale, H)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache_id: Optional[int], write_cache: bool) -> torch.Tensor:

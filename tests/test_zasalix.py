@@ -85,7 +85,7 @@ def test_run_order_and_cache_needs():
     assert groups[(("c", 1, 24), ("r", 1, 16))] == ([8], None, 0)
     assert groups[(("k", 2, 24), ("v", 2, 40))] == ([(1, "left"), (3, "left"), (5, "left")], 9, 4)
     assert groups[(("k", 2, 16), ("v", 2, 8))] == ([(7, "left")], 5, 7)
-    assert layout.states[(2, "memory")] == StateSpec((2, 40, 24), "float32")
+    assert layout.states[(2, "memory")] == StateSpec((2, 24, 40), "float32")  # kept column by column: [heads, vdim, dim]
     assert layout.states[(1, "right.normaliser")] == StateSpec((3, 16), "float32")
     assert layout.states[(5, "right.maximum")] == StateSpec((3,), "float32")
 

@@ -337,6 +337,35 @@ def test_an_open_forget_gate_carries_the_first_token_to_the_end(dtype):
     close(torch.cat(got), want, dtype, "portions", tol)
 
 
+def test_long_portions_of_the_memory_in_segments_side_by_side():
+    """bfloat16 portions long enough for the segmented scan (every segment from an empty memory, a carry through the
+    segments, then the walk that writes): two requests of unequal length side by side whose segments end inside a
+    portion, a single token between two long portions, and a request that enters with a state it built earlier.
+    Against the single walk on the same rounded projections the segments differ by float32 rounding only; against the
+    plain implementation both carry the projections' rounding, which the division by max(|n . q|, e^-m) enlarges
+    where n . q is a small difference of large terms."""
+    params = dict(MEMORY, hidden_size=32, num_heads=2, dim=40, vdim=24)
+    g = torch.Generator().manual_seed(62)
+    x_of = {"a": torch.randn(931, 32, generator=g).to(torch.bfloat16), "b": torch.randn(330, 32, generator=g).to(torch.bfloat16)}
+    results = {}
+    for form in ("walk", "segments"):
+        p = part("mixer", "mlstm", params)
+        bench = MixerBench(p, "bfloat16", page_size=8, pages=8, max_tokens=1024, seed=61)
+        assert p._segments is not None
+        if form == "walk":
+            p._segments = None
+        call = lambda rows, ctx, p=p: p.forward(rows.cuda().contiguous(), ctx, 0, True)  # noqa: E731
+        got = {"a": [], "b": []}
+        for step in ([("a", 3)], [("a", 600), ("b", 300)], [("a", 1), ("b", 1)], [("a", 327), ("b", 29)]):
+            for r, rows in bench.run(step, x_of, call).items():
+                got[r].append(rows)
+        results[form] = {r: torch.cat(rows) for r, rows in got.items()}
+    fn = plain_memory(params)
+    for r, x in x_of.items():
+        close(results["segments"][r], results["walk"][r], "bfloat16", f"request {r}: segments against the walk", tol=8e-3)
+        close(results["walk"][r], fn(x.double(), bench.ref, None)[0], "bfloat16", f"request {r}: the walk", tol=6e-2)
+
+
 @pytest.mark.parametrize("dtype", list(DT))
 @pytest.mark.parametrize("W,E,top,ff,shared,rows", [(40, 5, 2, 24, 32, 3), (40, 5, 2, 24, 32, 23), (64, 3, 3, 20, None, 40),
                                                      (128, 8, 2, 48, 64, 300), (136, 6, 1, 16, None, 700)])
