@@ -50,15 +50,17 @@ __global__ void add_dyt_kernel(float* __restrict__ stream, const T* __restrict__
   }
 }
 
-// grid (T).  p: [T, dim] in the compute dtype; side: float32 [T, ld], the layer's slice at column `col`.
+// A thread per value.  p: [T, dim] in the compute dtype; side: float32 [T, ld], the layer's slice at column `col`.
 template <typename T>
 __global__ void side_gate_kernel(const T* __restrict__ p, const float* __restrict__ side, int ld, int col,
-                                 T* __restrict__ out, int dim) {
+                                 T* __restrict__ out, int dim, long long total) {
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
-  for (int j = threadIdx.x; j < dim; j += blockDim.x)
-    out[(size_t)t * dim + j] = from_float<T>(gelu_tanh_f(to_float(p[(size_t)t * dim + j])) * side[(size_t)t * ld + col + j]);
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long t = i / dim;
+  const int j = (int)(i - t * dim);
+  out[i] = from_float<T>(gelu_tanh_f(to_float(p[i])) * side[t * ld + col + j]);
 }
 
 // grid (T), one block per row; the sum of squares in the block's fixed order.
@@ -79,17 +81,23 @@ __global__ void add_unit_rms_kernel(float* __restrict__ stream, const T* __restr
   for (int c = threadIdx.x; c < W; c += blockDim.x) stream[(size_t)t * W + c] += to_float(row[c]) * inv * w[c];
 }
 
-// grid (ceil(n / 256), T).  x: rows of ldx values, n of them from column 0; g: rows of ldg values, the gates'
-// pre-activations from column g_col.
-template <typename T>
+// grid (ceil(n / (256 * PER)), T).  x: rows of ldx values, n of them from column 0; g: rows of ldg values, the gates'
+// pre-activations from column g_col.  PER values per thread, as one access where the launcher found everything aligned.
+template <typename T, int PER>
 __global__ void sigmoid_gate_kernel(T* __restrict__ x, int ldx, const T* __restrict__ g, int ldg, int g_col, int n) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.y;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * PER;
   if (c >= n) return;
-  T* v = x + (size_t)t * ldx + c;
-  *v = from_float<T>(to_float(*v) * sigmoid_f(to_float(g[(size_t)t * ldg + g_col + c])));
+  struct alignas(sizeof(T) * PER) Pack { T v[PER]; };
+  T* xp = x + (size_t)t * ldx + c;
+  const T* gp = g + (size_t)t * ldg + g_col + c;
+  Pack xv = *reinterpret_cast<const Pack*>(xp);
+  const Pack gv = *reinterpret_cast<const Pack*>(gp);
+#pragma unroll
+  for (int i = 0; i < PER; ++i) xv.v[i] = from_float<T>(to_float(xv.v[i]) * sigmoid_f(to_float(gv.v[i])));
+  *reinterpret_cast<Pack*>(xp) = xv;
 }
 
 }  // namespace q3
@@ -109,7 +117,7 @@ extern "C" int q3_add_dyt(float* stream, const void* delta, const float* after_a
                           int dtype, int T, int W, cudaStream_t cuda_stream) {
   const int n = rows ? R : T;
   if (n <= 0) return 0;
-  if (W <= 0 || n > 65535 * 32) return Q3_ERR_SIZE;
+  if (W <= 0) return Q3_ERR_SIZE;
   const q3::DytParams after{after_alpha, after_w, after_b}, before{before_alpha, before_w, before_b};
   const dim3 grid((unsigned)((W + 1023) / 1024 > 0 ? (W + 1023) / 1024 : 1), (unsigned)n), block(256);
   if (n > 65535) return Q3_ERR_SIZE;
@@ -128,8 +136,10 @@ extern "C" int q3_side_gate(const void* p, const float* side, int ld, int col, v
                             cudaStream_t stream) {
   if (T <= 0) return 0;
   if (dim <= 0 || col < 0 || col + dim > ld) return Q3_ERR_SIZE;
-  Q3_BY_DTYPE(dtype, q3::launch(q3::side_gate_kernel<E>, dim3(T), dim3(dim >= 256 ? 256 : (dim >= 64 ? 64 : 32)), 0, stream,
-                                (const E*)p, side, ld, col, (E*)out, dim))
+  const long long total = (long long)T * dim;
+  if ((total + 255) / 256 > 0x7fffffffll) return Q3_ERR_SIZE;
+  Q3_BY_DTYPE(dtype, q3::launch(q3::side_gate_kernel<E>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream,
+                                (const E*)p, side, ld, col, (E*)out, dim, total))
   return q3::launch_status();
 }
 
@@ -147,7 +157,23 @@ extern "C" int q3_sigmoid_gate(void* x, int ldx, const void* g, int ldg, int g_c
                                cudaStream_t stream) {
   if (T <= 0 || n <= 0) return 0;
   if (T > 65535 || ldx < n || g_col < 0 || g_col + n > ldg) return Q3_ERR_SIZE;
-  Q3_BY_DTYPE(dtype, q3::launch(q3::sigmoid_gate_kernel<E>, dim3((n + 255) / 256, T), dim3(256), 0, stream, (E*)x, ldx,
+  // 16 bytes per access where the columns, the row pitches and the pointers allow it
+  const size_t es = dtype == Q3_F32 ? 4 : 2;
+  const int per = (int)(16 / es);
+  const bool wide = n % per == 0 && ldx % per == 0 && ldg % per == 0 && g_col % per == 0 && (uintptr_t)x % 16 == 0 &&
+                    (uintptr_t)g % 16 == 0;
+  if (wide) {
+    if (dtype == Q3_F32)
+      q3::launch(q3::sigmoid_gate_kernel<float, 4>, dim3((n / 4 + 255) / 256, T), dim3(256), 0, stream, (float*)x, ldx,
+                 (const float*)g, ldg, g_col, n);
+    else if (dtype == Q3_BF16)
+      q3::launch(q3::sigmoid_gate_kernel<__nv_bfloat16, 8>, dim3((n / 8 + 255) / 256, T), dim3(256), 0, stream,
+                 (__nv_bfloat16*)x, ldx, (const __nv_bfloat16*)g, ldg, g_col, n);
+    else
+      return Q3_ERR_DTYPE;
+    return q3::launch_status();
+  }
+  Q3_BY_DTYPE(dtype, q3::launch(q3::sigmoid_gate_kernel<E, 1>, dim3((n + 255) / 256, T), dim3(256), 0, stream, (E*)x, ldx,
                                 (const E*)g, ldg, g_col, n))
   return q3::launch_status();
 }
