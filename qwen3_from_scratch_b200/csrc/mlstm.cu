@@ -295,14 +295,14 @@ mlstm_scan_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col, int 
 #pragma unroll
       for (int j = 0; j < PER; ++j) {
         const int d = lane + 32 * j;
-        const float kd = k_s[c * DP + d], qd = q_s[c * DP + d];
+        const float kd = k_s[c * DP + d], qd = MODE == ML_LOCAL ? 0.f : q_s[c * DP + d];
         const float tk = take * kd;
         n[j] = fmaf(keep, n[j], tk);
-        nq[c] = fmaf(n[j], qd, nq[c]);
+        if (MODE != ML_LOCAL) nq[c] = fmaf(n[j], qd, nq[c]);  // a segment alone writes no outputs
 #pragma unroll
         for (int i = 0; i < CPT; ++i) {
           S[i][j] = fmaf(keep, S[i][j], tk * vc[i]);
-          num[c][i] = fmaf(S[i][j], qd, num[c][i]);
+          if (MODE != ML_LOCAL) num[c][i] = fmaf(S[i][j], qd, num[c][i]);
         }
       }
     }
