@@ -396,7 +396,7 @@ class SandwichNormBlock(Block):
             specs += [WeightSpec(f"{self.side_prefix}.gate", (d, self.width)),
                       WeightSpec(f"{self.side_prefix}.proj", (self.width, d)),
                       WeightSpec(f"{self.side_prefix}.norm", (self.width,), kind="vector", init="one_plus_normal")]
-        if self.entry and self.entry.get("declares", True):
+        if self.entry:
             specs.append(WeightSpec(self.entry["step"], (int(self.entry["times"]), self.width), kind="vector", init="normal"))
         return specs
 
