@@ -445,7 +445,7 @@ def test_model_whole_decoded_and_in_portions(folders, key, dtype):
 
 
 @pytest.mark.parametrize("dtype", list(DT))
-@pytest.mark.parametrize("key", ["x", "z"])
+@pytest.mark.parametrize("key", ["x", "z", "w"])
 def test_unequal_requests_together_equal_each_alone_with_pages_and_slots_used_again(folders, key, dtype):
     """Five requests through two state slots and a pool that holds less than their sum: portions of some beside
     single tokens of others; a slot and its pages go to the next request as soon as one ends; pages that fall out of

@@ -73,7 +73,17 @@ ZASALIX_Z = {
                         moe(8, 2, 48, 96)),
                with_mlp(parallel(4, 1, 128, 32, 0.09, 20, 33, 10000.0, 32, memory(2, 128, 32, 12.0)), dense(256)),
                with_mlp(latent(4, 32, 32, 64, 64, 96, 0.12, 50000.0), moe(12, 4, 32, 64))]}
-CONFIGS = {"x": (ZASALIX_X, 3), "y": (ZASALIX_Y, 4), "z": (ZASALIX_Z, 5)}
+# W: sizes that are multiples of 8 but not of 16 or 32: five heads, keys of 80 and values of 112, a latent of 128 (a
+# size the tensor-core kernel takes) with a rotated part of 24, a window of 40 that keeps 12, experts of 80; the loop is
+# the first two layers, the model ends with two latent attentions of different sizes.
+ZASALIX_W = {
+    "architecture": "Zasalix", "vocab": 400, "width": 160, "norm": {"eps": 1e-6}, "token_side": {"dim": 24},
+    "loop": {"start": 0, "stop": 2, "times": 2},
+    "layers": [with_mlp(parallel(5, 5, 80, 112, 0.1, 40, 12, 20000.0, 40, memory(5, 24, 56, 12.0), 1.2, 0.5), moe(6, 2, 80, 48)),
+               with_mlp(memory(3, 56, 40, 9.0), dense(200)),
+               with_mlp(latent(5, 48, 24, 40, 128, 96, 0.12, 500000.0), moe(4, 1, 48)),
+               with_mlp(latent(3, 64, 8, 56, 72, 104, 0.11, 10000.0, dims=8), None)]}
+CONFIGS = {"x": (ZASALIX_X, 3), "y": (ZASALIX_Y, 4), "z": (ZASALIX_Z, 5), "w": (ZASALIX_W, 6)}
 
 
 def tensor_shapes(config: dict) -> Dict[str, tuple]:
