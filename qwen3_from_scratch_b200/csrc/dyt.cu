@@ -50,6 +50,64 @@ __global__ void add_dyt_kernel(float* __restrict__ stream, const T* __restrict__
   }
 }
 
+// The same four features at a time: 16-byte accesses of the float32 arrays, 8-byte ones of bfloat16 (W a multiple of
+// 4, every pointer aligned; the launcher sees to it).  The arithmetic of a feature is add_dyt_kernel's.
+__device__ __forceinline__ void load4f(const float* p, float (&x)[4]) {
+  const float4 v = *reinterpret_cast<const float4*>(p);
+  x[0] = v.x, x[1] = v.y, x[2] = v.z, x[3] = v.w;
+}
+__device__ __forceinline__ void load4f(const __nv_bfloat16* p, float (&x)[4]) {
+  const uint2 v = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  x[0] = a.x, x[1] = a.y, x[2] = b.x, x[3] = b.y;
+}
+__device__ __forceinline__ void store4f(float* p, const float (&x)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(x[0], x[1], x[2], x[3]);
+}
+__device__ __forceinline__ void store4f(__nv_bfloat16* p, const float (&x)[4]) {
+  uint2 v;
+  *reinterpret_cast<__nv_bfloat162*>(&v.x) = __floats2bfloat162_rn(x[0], x[1]);
+  *reinterpret_cast<__nv_bfloat162*>(&v.y) = __floats2bfloat162_rn(x[2], x[3]);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
+template <typename T, typename O>
+__global__ void add_dyt4_kernel(float* __restrict__ stream, const T* __restrict__ delta, DytParams after,
+                                const float* __restrict__ rows_add, const float* __restrict__ vec_add, DytParams before,
+                                O* __restrict__ out, const int* __restrict__ rows, int W) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.y;
+  const int t = rows ? rows[r] : r;
+  const float a_after = after.alpha ? *after.alpha : 0.f, a_before = before.alpha ? *before.alpha : 0.f;
+  for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4; c < W; c += gridDim.x * blockDim.x * 4) {
+    const size_t i = (size_t)t * W + c;
+    float x[4], y[4];
+    load4f(stream + i, x);
+    if (delta) {
+      load4f(delta + i, y);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] += after.alpha ? dyt(y[k], a_after, after.w, after.b, c + k) : y[k];
+    }
+    if (rows_add) {
+      load4f(rows_add + i, y);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] += y[k];
+    }
+    if (vec_add) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[k] += vec_add[c + k];
+    }
+    if (!rows) store4f(stream + i, x);
+    if (out) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) y[k] = before.alpha ? dyt(x[k], a_before, before.w, before.b, c + k) : x[k];
+      store4f(out + (size_t)r * W + c, y);
+    }
+  }
+}
+
 // A thread per value.  p: [T, dim] in the compute dtype; side: float32 [T, ld], the layer's slice at column `col`.
 template <typename T>
 __global__ void side_gate_kernel(const T* __restrict__ p, const float* __restrict__ side, int ld, int col,
@@ -121,6 +179,19 @@ extern "C" int q3_add_dyt(float* stream, const void* delta, const float* after_a
   const q3::DytParams after{after_alpha, after_w, after_b}, before{before_alpha, before_w, before_b};
   const dim3 grid((unsigned)((W + 1023) / 1024 > 0 ? (W + 1023) / 1024 : 1), (unsigned)n), block(256);
   if (n > 65535) return Q3_ERR_SIZE;
+  const bool by4 = W % 4 == 0 && (uintptr_t)stream % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)rows_add % 16 == 0 &&
+                   (uintptr_t)out % 16 == 0;
+  if (by4) {  // the same arithmetic, four features per access
+    if (out_f32) {
+      Q3_BY_DTYPE(dtype, q3::launch(q3::add_dyt4_kernel<E, float>, grid, block, 0, cuda_stream, stream, (const E*)delta,
+                                    after, rows_add, vec_add, before, (float*)out, rows, W))
+    } else {
+      Q3_BY_DTYPE(dtype, q3::launch(q3::add_dyt4_kernel<E, E>, grid, block, 0, cuda_stream, stream, (const E*)delta, after,
+                                    rows_add, vec_add, before, (E*)out, rows, W))
+    }
+    if (!rows) q3::note_stream_written();
+    return q3::launch_status();
+  }
   if (out_f32) {
     Q3_BY_DTYPE(dtype, q3::launch(q3::add_dyt_kernel<E, float>, grid, block, 0, cuda_stream, stream, (const E*)delta, after,
                                   rows_add, vec_add, before, (float*)out, rows, W))
