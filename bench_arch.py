@@ -425,6 +425,11 @@ def compare(args, peaks, sample_clocks):
             out[model][name] = run_scenario(config, scenario, args.steps, args.warmup, peaks)
             print(f"[bench] {model} {name}: {out[model][name]['ms_per_step']} ms", file=sys.stderr, flush=True)
     out["clocks"] = sampler.stop()
+    # the sampler runs from before the models are made: where making them takes long most samples see an idle GPU, so the
+    # median of the samples taken under load (at half of the top clock or more) is given beside the median of all
+    busy = [s[0] for s in getattr(sampler, "samples", []) if s[1] and s[0] >= 0.5 * s[1]]
+    out["clocks"]["sm_mhz_under_load"] = statistics.median(busy) if busy else None
+    out["clocks"]["samples_under_load"] = len(busy)
     out["seconds"] = round(time.time() - t0, 1)
     print(json.dumps(out))
     return 0
