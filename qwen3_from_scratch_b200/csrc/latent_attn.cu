@@ -12,8 +12,8 @@
 // Rotation: dimension i of the first `dims` of a rotated part is paired with i + dims / 2 (`pairing` 0, halves) or
 // dimension 2i with 2i + 1 (`pairing` 1, neighbours); the angle is position * freq[i] in float32 and sine and cosine
 // are multiplied by `mag` (the frequencies and the magnitude carry whatever stretching the model uses; the kernel
-// only applies them).  A sink (`sink`, one number per head, or null) is a term exp(sink_h) in the softmax's
-// denominator that has no key and no value and is not scaled.
+// only applies them).  A sink (`sink`, one logit per head, or null) takes part in the softmax's denominator only:
+// weights exp(s_j) / (sum_j exp(s_j) + exp(sink_h)), with the scale on the scores s_j and not on the sink.
 #include "common.cuh"
 
 namespace q3 {

@@ -1516,7 +1516,7 @@ def latent_attn_ref(q_abs: torch.Tensor, q_rot: torch.Tensor, c_pages: torch.Ten
     """Causal softmax attention over latents: q_abs float32 [H, T, rank] (the plain query taken through the key
     up-projection), q_rot [T, H, rot]; score = (q_abs . c + q_rot . r) * scale over the keys 0 .. position of the
     token's request; out [T, H * rank] = sum_j p_j c_j.  A warp per (token, head), keys one by one.  ``sink``: float32
-    [H] or None: exp(sink_h) joins the denominator of head h's softmax (no key, no value, not scaled)."""
+    [H] or None: head h's weights are exp(s_j) / (sum_j exp(s_j) + exp(sink_h)), the scale on the scores only."""
     _check("latent_attn_ref.q_abs", q_abs, torch.float32)
     _check("latent_attn_ref.q_rot", q_rot)
     _check("latent_attn_ref.c_pages", c_pages, q_rot.dtype)

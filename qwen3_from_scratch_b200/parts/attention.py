@@ -241,8 +241,9 @@ class LatentAttention(Mixer):
         score(head) = (q_plain . W_uk,head c + q_rot . r) * scale;   value(head) = W_uv,head c
         out = W_o concat_heads(sigmoid(W_g h)_head * softmax(scores) values)
 
-    ``gate=False``: no W_g, the heads' outputs go to W_o as they are.  ``sink=True``: a learned number per head
-    (``<name>.sink``) whose exponential joins the softmax's denominator: it has no key and no value and is not scaled.
+    ``gate=False``: no W_g, the heads' outputs go to W_o as they are.  ``sink=True``: a learned logit per head
+    (``<name>.sink``) that takes part in the softmax's denominator only, weights = exp(s_j) / (sum_j exp(s_j) + exp(sink)):
+    nothing is scored for it, nothing is weighted by it, and ``scale`` is not applied to it.
     ``pairing``: which values of a rotated part turn together, "halves" (i with i + dims / 2) or "neighbours" (2i with
     2i + 1); the frequencies are the position part's either way.
 
