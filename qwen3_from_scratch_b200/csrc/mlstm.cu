@@ -143,7 +143,9 @@ __global__ void mlstm_carry_kernel(const int* __restrict__ first_of, const int* 
 }
 
 template <typename T, int PER, int CPT, int CHUNK, int MODE>
-__global__ void __launch_bounds__(ML_THREADS)
+// the segments' walks at four blocks to an SM (128 registers: a long prompt's segments then run in two rounds instead of
+// three); the single walk, bound by the latency of its own chain, keeps the registers it wants
+__global__ void __launch_bounds__(ML_THREADS, MODE == ML_PLAIN ? 1 : 4)
 mlstm_scan_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col, int v_col, int i_col, int f_col,
                   const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap, float q_scale,
                   float* __restrict__ S_state, float* __restrict__ n_state, float* __restrict__ m_state,
@@ -299,10 +301,17 @@ mlstm_scan_kernel(const T* __restrict__ proj, int ld, int q_col, int k_col, int 
         const float tk = take * kd;
         n[j] = fmaf(keep, n[j], tk);
         if (MODE != ML_LOCAL) nq[c] = fmaf(n[j], qd, nq[c]);  // a segment alone writes no outputs
+        // two columns per instruction (the packed float32 multiply-add of sm_100): the same roundings as one by one
+        const float2 keep2 = make_float2(keep, keep), tk2 = make_float2(tk, tk), qd2 = make_float2(qd, qd);
 #pragma unroll
-        for (int i = 0; i < CPT; ++i) {
-          S[i][j] = fmaf(keep, S[i][j], tk * vc[i]);
-          if (MODE != ML_LOCAL) num[c][i] = fmaf(S[i][j], qd, num[c][i]);
+        for (int i = 0; i < CPT; i += 2) {
+          float2 s2 = make_float2(S[i][j], S[i + 1][j]);
+          s2 = __ffma2_rn(keep2, s2, __fmul2_rn(tk2, make_float2(vc[i], vc[i + 1])));
+          S[i][j] = s2.x, S[i + 1][j] = s2.y;
+          if (MODE != ML_LOCAL) {
+            const float2 n2 = __ffma2_rn(s2, qd2, make_float2(num[c][i], num[c][i + 1]));
+            num[c][i] = n2.x, num[c][i + 1] = n2.y;
+          }
         }
       }
     }
