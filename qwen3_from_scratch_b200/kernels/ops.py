@@ -2277,13 +2277,27 @@ def mlstm_max_dim() -> int:
 
 
 MLSTM_SEGMENT = 128       # tokens of a segment of the segmented scan
-MLSTM_SEGMENTED_FROM = 256  # the longest portion of a step from which the segments pay
+MLSTM_SEGMENTED_FROM = 256  # the longest portion of a step from which the segments can pay
+# measured on a B200 (keys of 128, values of 256, 4 and 8 heads; keys of 32, values of 48): the single walk takes
+# 0.43 us a token whatever the sizes (one warp per scheduler, bound by its own chain); the segmented form's two walks
+# take 6.5e-7 us per token and value of the memory (bound by issue), and its list and carry some 30 us
+MLSTM_WALK_US_PER_TOKEN = 0.43
+MLSTM_SEGMENTS_US_PER_TOKEN_VALUE = 6.5e-7
+MLSTM_SEGMENTS_FIXED_US = 30.0
 
 
-def mlstm_segmented_pays(dtype: torch.dtype, max_q_len: int) -> bool:
+def mlstm_segmented_pays(dtype: torch.dtype, max_q_len: int, num_tokens: Optional[int] = None,
+                         memory_values: Optional[int] = None) -> bool:
     """Whether a step runs the scan in segments side by side: bfloat16 (the float32 run keeps the single walk, whose sums
-    have one order whatever the cut) and a portion long enough to be cut."""
-    return dtype == torch.bfloat16 and max_q_len >= MLSTM_SEGMENTED_FROM
+    have one order whatever the cut), a portion long enough to be cut, and (given the step's tokens and heads * dim * vdim)
+    the walk of the longest portion slower than both walks of all tokens: several long portions already run side by
+    side in the single walk."""
+    if dtype != torch.bfloat16 or max_q_len < MLSTM_SEGMENTED_FROM:
+        return False
+    if num_tokens is None or memory_values is None:
+        return True
+    return (MLSTM_WALK_US_PER_TOKEN * max_q_len
+            > MLSTM_SEGMENTS_FIXED_US + MLSTM_SEGMENTS_US_PER_TOKEN_VALUE * num_tokens * memory_values)
 
 
 class MlstmScratch:
@@ -2322,7 +2336,7 @@ def mlstm_scan(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, i_col: in
             or max(q_col + H * D, k_col + H * D, v_col + H * Dv, i_col + H, f_col + H) > ld):
         raise KernelError(f"mlstm_scan: proj {tuple(proj.shape)}, memory {tuple(memory.shape)}, out {tuple(out.shape)}")
     seg, max_segments, extra = 0, 0, [None] * 5
-    if scratch is not None and mlstm_segmented_pays(proj.dtype, max_q_len):
+    if scratch is not None and mlstm_segmented_pays(proj.dtype, max_q_len, T, H * D * Dv):
         seg, max_segments = MLSTM_SEGMENT, T // MLSTM_SEGMENT + int(num_seqs)
         if (max_segments > scratch.max_segments or scratch.memory.numel() < max_segments * H * Dv * D
                 or scratch.first_of.numel() < num_seqs + 1):
